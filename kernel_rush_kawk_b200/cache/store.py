@@ -37,12 +37,16 @@ class KVView:
     """What a mixer's kernels get: this run's pages and its group's page table."""
 
     k: torch.Tensor  # [pages, kv_heads, PAGE, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor  # [pages, kv_heads, PAGE, v_dim]; v_dim is head_dim unless the need says otherwise
     table: torch.Tensor  # int32 [slots, width] on the device
     width: int  # logical pages per slot; position p is in table[slot, (p // PAGE) % width]
     window: int | None
     kv_heads: int
     head_dim: int
+    v_dim: int = 0
+
+    def __post_init__(self):
+        self.v_dim = self.v_dim or self.head_dim
 
 
 @dataclass
@@ -59,13 +63,13 @@ class _KVGroup:
         self.ledger = PageLedger(n_pages, n_slots, self.width, PAGE, ring)
         shape = (len(runs), n_pages, need.kv_heads, PAGE, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape[:-1] + (need.v_dim or need.head_dim,), dtype=dtype, device=device)
         self.table_host = np.zeros((n_slots, self.width), dtype=np.int32)
         self.table = torch.zeros((n_slots, self.width), dtype=torch.int32, device=device)
         self.dirty: set[int] = set()
 
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 class _StateGroup:
@@ -77,8 +81,9 @@ class _StateGroup:
 
 
 class SequenceCache:
-    """needs: one entry per schedule run: KVNeed, StateNeed, None, or ("from", j) for
-    a run that reads run j's storage.
+    """needs: one entry per schedule run: KVNeed, StateNeed, None, ("from", j) for
+    a run that reads run j's storage, or a tuple of KVNeed / StateNeed for a run that
+    keeps several kinds of storage (its view is then a tuple of views in that order).
 
     max_tokens: positions all live sequences may hold together, each sequence's
     count rounded up to whole pages. max_slots: live sequences. max_context: the
@@ -99,13 +104,20 @@ class SequenceCache:
         self.h2d_bytes = 0  # page-table rows (and their indices) copied to the device so far
         self._kv_groups: list[_KVGroup] = []
         self._state_groups: list[_StateGroup] = []
-        self._where: list = [None] * len(needs)  # run -> (group, line) or None
+        self._where: list = [None] * len(needs)  # run -> (group, line), a list of them, or None
 
         by_need: dict = {}
+        several: dict = {}  # run -> its needs, for runs that keep more than one kind of storage
         for run, need in enumerate(needs):
             if isinstance(need, (KVNeed, StateNeed)):
-                by_need.setdefault(need, []).append(run)
-        for need, runs in by_need.items():
+                by_need.setdefault(need, []).append((run, None))
+            elif isinstance(need, (tuple, list)) and need and all(isinstance(n, (KVNeed, StateNeed)) for n in need):
+                several[run] = list(need)
+                self._where[run] = [None] * len(need)
+                for k, n in enumerate(need):
+                    by_need.setdefault(n, []).append((run, k))
+        for need, users in by_need.items():
+            runs = [run for run, _ in users]
             if isinstance(need, KVNeed):
                 ring = None
                 pages = self.n_pages
@@ -117,12 +129,15 @@ class SequenceCache:
             else:
                 group = _StateGroup(need, runs, self.max_slots, self.device, dtype)
                 self._state_groups.append(group)
-            for line, run in enumerate(runs):
-                self._where[run] = (group, line)
+            for line, (run, k) in enumerate(users):
+                if k is None:
+                    self._where[run] = (group, line)
+                else:
+                    self._where[run][k] = (group, line)
         for run, need in enumerate(needs):
             if isinstance(need, tuple) and need and need[0] == "from":
                 src = self._where[need[1]]
-                if src is None or not isinstance(src[0], _KVGroup):
+                if src is None or isinstance(src, list) or not isinstance(src[0], _KVGroup):
                     raise CacheError(f"run {run} reads the cache of run {need[1]}, which keeps no keys and values")
                 self._where[run] = src
 
@@ -191,10 +206,15 @@ class SequenceCache:
         where = self._where[run]
         if where is None:
             return None
-        group, line = where
+        if isinstance(where, list):
+            return tuple(self._view_of(group, line) for group, line in where)
+        return self._view_of(*where)
+
+    @staticmethod
+    def _view_of(group, line):
         if isinstance(group, _KVGroup):
             return KVView(group.k[line], group.v[line], group.table, group.width, group.need.window,
-                          group.need.kv_heads, group.need.head_dim)
+                          group.need.kv_heads, group.need.head_dim, group.need.v_dim or group.need.head_dim)
         return StateView(group.state[line])
 
     # -- accounting ---------------------------------------------------------

@@ -47,9 +47,12 @@ def get_architecture(name: str) -> Architecture:
 
 def architecture_name(raw: dict) -> str:
     names = raw.get("architectures")
-    if not names or not isinstance(names, (list, tuple)):
-        raise ConfigError("config.json lacks 'architectures' (a list with the model class name)")
-    return str(names[0])
+    if names and isinstance(names, (list, tuple)):
+        return str(names[0])
+    name = raw.get("architecture")  # some designs name themselves with one string
+    if isinstance(name, str) and name:
+        return name
+    raise ConfigError("config.json lacks 'architectures' (a list with the model class name) or 'architecture' (its name)")
 
 
 def read_config(folder_or_dict) -> tuple[Architecture, ModelConfig]:
@@ -89,4 +92,4 @@ def _load_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from ..models import qwen3  # noqa: F401  (registers itself on import)
+        from ..models import qwen3, taredra  # noqa: F401  (each registers itself on import)

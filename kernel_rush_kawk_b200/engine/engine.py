@@ -29,7 +29,7 @@ import torch
 from ..cache.store import PAGE, SequenceCache
 from ..config.registry import get_architecture, preset_config, read_config
 from ..sampling.sampler import Sampler, SamplingParams
-from ..weights.loader import read_checkpoint
+from ..weights.loader import checkpoint_shapes, read_checkpoint
 from ..weights.random_init import random_tensors
 from .generate import GenerationLoop, pages_needed
 from .model import Model, PartTree, Runtime
@@ -78,11 +78,13 @@ class Engine:
             if model_path is None:
                 raise ValueError("Engine needs a model folder (or use Engine.from_random)")
             self.architecture, self.config = read_config(model_path)
+            if hasattr(self.config, "with_tensor_shapes"):  # sizes that only the tensors give
+                self.config = self.config.with_tensor_shapes(checkpoint_shapes(model_path))
         self.model_path = None if model_path is None else Path(model_path)
         self.plan = self.architecture.plan(self.config)
         self.max_context = min(int(max_context or self.plan.max_positions), self.plan.max_positions)
         tree = PartTree(self.plan, self.max_context)
-        head_dims = sorted({n.head_dim for n in tree.cache_needs() if hasattr(n, "head_dim")})
+        head_dims = tree.attention_head_dims()
         self.ops = ops if ops is not None else _default_ops(self.device, head_dims)
         expected = tree.expected_tensors()
         if _tensors is None:

@@ -57,12 +57,17 @@ class PartTree:
         for spec in plan.layers:
             mixer_norm = _build(spec.mixer_norm, parts_base.norm_class)
             mixer = _build(spec.mixer, parts_base.mixer_class)
-            ffn_norm = _build(spec.feed_forward_norm, parts_base.norm_class)
-            ffn = _build(spec.feed_forward, parts_base.feed_forward_class)
+            built = [mixer_norm, mixer]
+            ffn_norm = ffn = None
+            if spec.feed_forward is not None:
+                ffn_norm = _build(spec.feed_forward_norm, parts_base.norm_class)
+                ffn = _build(spec.feed_forward, parts_base.feed_forward_class)
+                built += [ffn_norm, ffn]
             if self.position is not None and hasattr(mixer.part, "set_position"):
                 mixer.part.set_position(self.position.part)
-            block = parts_base.block_class(spec.block)(mixer_norm.part, mixer.part, ffn_norm.part, ffn.part)
-            self.layers.append((block, [mixer_norm, mixer, ffn_norm, ffn]))
+            block = parts_base.block_class(spec.block)(mixer_norm.part, mixer.part, ffn_norm and ffn_norm.part,
+                                                       ffn and ffn.part)
+            self.layers.append((block, built))
         for i, entry in enumerate(plan.schedule):
             mixer = self.layers[entry.layer][0].mixer
             owns = getattr(mixer, "own_cache", True)
@@ -95,6 +100,13 @@ class PartTree:
                 expected.setdefault(name, tspec)
         return expected
 
+    def attention_head_dims(self) -> list[int]:
+        """Head sizes whose per-size attention libraries this model's mixers call."""
+        dims = set()
+        for block, _ in self.layers:
+            dims.update(getattr(block.mixer, "attention_head_dims", lambda: ())())
+        return sorted(dims)
+
     def cache_needs(self) -> list:
         needs = []
         for entry in self.plan.schedule:
@@ -125,7 +137,8 @@ class Model:
         self.position = self.tree.position.part if self.tree.position is not None else None
         self.blocks = [block for block, _ in self.tree.layers]
         self.graph_safe = all(getattr(part, "graph_safe", False) for block in self.blocks
-                              for part in (block.mixer_norm, block.mixer, block.feed_forward_norm, block.feed_forward))
+                              for part in (block.mixer_norm, block.mixer, block.feed_forward_norm, block.feed_forward)
+                              if part is not None)
         if self.position is not None:
             self.graph_safe = self.graph_safe and getattr(self.position, "graph_safe", False)
 

@@ -11,5 +11,9 @@ from .attention import GQAttention
 from .mlp import SwiGLU
 from .block import PreNormBlock
 from .embedding import OutputHead, TokenEmbedding
+from .wide import GatedMLP, ScaledEmbedding, WideRMSNorm
+from .branches import Branch, ParallelMixer
+from .sink_attention import SinkWindowAttention
+from .recurrent import DeltaRule, TimeMixWKV
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -64,6 +64,9 @@ class GQAttention(Mixer):
     def cache_need(self):
         return KVNeed(self.kv_heads, self.head_dim, self.window)
 
+    def attention_head_dims(self):
+        return (self.head_dim,)
+
     def set_position(self, position) -> None:
         self.position = position
 

@@ -45,6 +45,8 @@ class KVNeed:
     kv_heads: int
     head_dim: int
     window: int | None = None
+    #: size of a value head where it differs from the key head's (None: the same)
+    v_dim: int | None = None
 
 
 @dataclass(frozen=True)
@@ -100,12 +102,14 @@ class Head(Part):
 
 class Mixer(Part):
     def cache_need(self):
-        """KVNeed, StateNeed or None."""
+        """KVNeed, StateNeed, None, or a tuple of them for a mixer that keeps several
+        kinds of storage (keys and values beside a recurrent state, say)."""
         return None
 
     def forward(self, ctx, h, cache):
         """h [rows, hidden] normalised input -> branch [rows, hidden]. ``cache`` is
-        the view of this run's storage (None if ``cache_need`` is None)."""
+        the view of this run's storage (None if ``cache_need`` is None, a tuple of
+        views in the order of the needs if it is a tuple)."""
         raise NotImplementedError
 
 
@@ -129,9 +133,10 @@ class PositionEncoding(Part):
 
 
 class Block:
-    """Arrangement of a layer's parts around the residual stream."""
+    """Arrangement of a layer's parts around the residual stream. A layer without a
+    feed-forward has None for it and for its norm."""
 
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, feed_forward_norm: Norm, feed_forward: FeedForward):
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, feed_forward_norm: Norm | None, feed_forward: FeedForward | None):
         self.mixer_norm = mixer_norm
         self.mixer = mixer
         self.feed_forward_norm = feed_forward_norm

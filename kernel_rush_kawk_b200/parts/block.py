@@ -17,6 +17,8 @@ class PreNormBlock(Block):
         branch = self.mixer.forward(ctx, h, cache)
         h.tensor()  # a mixer that never looked at its input still moves the stream on
         stream.branch = branch
+        if self.feed_forward is None:
+            return stream
 
         h = self.feed_forward_norm.forward(ctx, stream)
         branch = self.feed_forward.forward(ctx, h)

@@ -40,13 +40,13 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One layer: a block arrangement over a mixer and a feed-forward, each behind
-    its own norm."""
+    its own norm. A layer that has a mixer only leaves both feed-forward entries None."""
 
     block: str  # registered arrangement, e.g. "prenorm"
     mixer_norm: PartSpec
     mixer: PartSpec
-    feed_forward_norm: PartSpec
-    feed_forward: PartSpec
+    feed_forward_norm: PartSpec | None = None
+    feed_forward: PartSpec | None = None
 
 
 @dataclass(frozen=True)

@@ -1,0 +1,82 @@
+"""Grouped-query attention over a sliding window with a softmax sink.
+
+q = Wq h, k = Wk h, v = Wv h (no biases); the first ``rot_dims`` elements of every
+q and k head are rotated by the position (element i with element i + rot_dims/2,
+angle p * rot_base^(-2i/rot_dims), positions and angles in 32-bit); with
+``value_norm`` every value head is divided by its root mean square before it is
+cached; a query at position p sees keys p - window + 1 .. p (``window`` None: all
+of 0..p); score = (q . k) * scale with ``scale`` a parameter; with ``sink`` each
+head's softmax has one more term in its denominator, exp(sink_h), which carries
+no value. Key and value heads may differ in size (``dim``, ``vdim``). Scores and
+weights are 32-bit; the weights multiply the values unrounded.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .base import KVNeed, TensorSpec, register_mixer
+from .branches import Branch
+
+
+class SinkWindowAttention(Branch):
+    """params: hidden, heads, kv_heads, dim, vdim, scale, window (None or int), rot_dims, rot_base,
+    value_norm (bool), sink (bool), eps."""
+
+    def __init__(self, params):
+        super().__init__(params)
+        p = params
+        self.hidden = int(p["hidden"])
+        self.heads = int(p["heads"])
+        self.kv_heads = int(p["kv_heads"])
+        self.dim = int(p["dim"])
+        self.vdim = int(p.get("vdim") or self.dim)
+        self.scale = float(p["scale"])
+        self.window = None if p.get("window") is None else int(p["window"])
+        self.rot_dims = int(p.get("rot_dims", 0))
+        self.rot_base = float(p.get("rot_base", 10000.0))
+        self.value_norm = bool(p.get("value_norm", False))
+        self.has_sink = bool(p.get("sink", False))
+        self.eps = float(p.get("eps", 0.0))
+        if self.heads % self.kv_heads:
+            raise ValueError(f"heads ({self.heads}) must be a multiple of kv_heads ({self.kv_heads})")
+        if self.rot_dims % 2 or self.rot_dims > self.dim:
+            raise ValueError(f"rot_dims ({self.rot_dims}) must be even and at most dim ({self.dim})")
+
+    def tensor_specs(self):
+        specs = {"q": TensorSpec((self.heads * self.dim, self.hidden)),
+                 "k": TensorSpec((self.kv_heads * self.dim, self.hidden)),
+                 "v": TensorSpec((self.kv_heads * self.vdim, self.hidden)),
+                 "o": TensorSpec((self.hidden, self.heads * self.vdim))}
+        if self.has_sink:
+            specs["sink"] = TensorSpec((self.heads,), "vector")
+        return specs
+
+    def cache_need(self):
+        return KVNeed(self.kv_heads, self.dim, self.window, None if self.vdim == self.dim else self.vdim)
+
+    def bind(self, tensors, runtime):
+        self.w = {k: tensors[k] for k in ("q", "k", "v", "o")}
+        self.sink = tensors["sink"].float().contiguous() if self.has_sink else None
+        # the few rotation frequencies come from the host in 64-bit, so that they depend on no device's pow()
+        i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
+        self.inv_freq = (self.rot_base ** (-2.0 * i / max(self.rot_dims, 1))).to(torch.float32).to(runtime.device)
+        self.bind_standalone()
+
+    def in_weight(self):
+        return torch.cat([self.w["q"], self.w["k"], self.w["v"]], dim=0)
+
+    def out_weight(self):
+        return self.w["o"]
+
+    def middle(self, ctx, proj, cache, out, col0, scale):
+        ops = ctx.ops
+        k_col = self.heads * self.dim
+        v_col = k_col + self.kv_heads * self.dim
+        ops.rotate_norm_write(proj, 0, k_col, v_col, self.heads, self.kv_heads, self.dim, self.vdim, self.inv_freq,
+                              self.rot_dims, self.eps if self.value_norm else None, ctx.batch, cache)
+        ops.sink_attention(proj, 0, self.heads, self.dim, self.vdim, self.sink, self.scale, self.window, ctx.batch, cache,
+                           out, col0, scale)
+
+
+register_mixer("sink_window_attention", SinkWindowAttention)

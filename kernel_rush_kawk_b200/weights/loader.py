@@ -58,6 +58,21 @@ def stored_dtype(role: str, ndim: int, file_dtype: torch.dtype, compute: torch.d
     return compute
 
 
+def checkpoint_shapes(folder) -> dict[str, tuple]:
+    """Tensor name -> shape over every shard of a folder, from the files' headers alone."""
+    from safetensors import safe_open
+
+    shapes: dict[str, tuple] = {}
+    for shard in sorted(Path(folder).glob("*.safetensors")):
+        try:
+            with safe_open(str(shard), framework="pt", device="cpu") as f:
+                for name in f.keys():
+                    shapes.setdefault(name, tuple(f.get_slice(name).get_shape()))
+        except Exception as exc:
+            raise WeightError(folder, [], [], {}, [f"{shard.name} cannot be read: {exc}"]) from exc
+    return shapes
+
+
 def read_checkpoint(folder, expected: dict, device, compute: torch.dtype, duplicates=None) -> dict[str, torch.Tensor]:
     """expected: full tensor name -> TensorSpec. Returns name -> tensor on ``device``."""
     from safetensors import safe_open

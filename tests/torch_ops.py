@@ -154,3 +154,141 @@ class TorchOps:
             g = -torch.log(-torch.log(u))
             out[r] = int(torch.argmax(logits[r].cpu() / temperature + g))
         return out.to(logits.device)
+
+
+# ----------------------------------------------------------------------------
+# the kernels of models with a 32-bit residual stream, windowed attention with a sink,
+# and recurrent state (kernel_rush_kawk_b200/csrc/wide_rows.cu, sink_attention.cu, recurrent.cu)
+# ----------------------------------------------------------------------------
+
+def _act(z, name):
+    if name == "silu":
+        return z * torch.sigmoid(z)
+    if name == "sigmoid":
+        return torch.sigmoid(z)
+    if name == "gelu_tanh":
+        return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+    raise ValueError(name)
+
+
+class _WideOps:
+    def embed_scaled(self, table, tokens, n_rows, scale):
+        return table[tokens.long()].float() * scale
+
+    def rmsnorm_wide(self, x, branch, gain, offset, eps, x_new, out_dtype):
+        s = x if branch is None else x + branch.float()
+        if branch is not None:
+            x_new.copy_(s)
+        return (s * torch.rsqrt((s * s).mean(dim=-1, keepdim=True) + eps) * (offset + gain.float())).to(out_dtype)
+
+    def gate_up_act(self, h, w_gate_up, intermediate, activation):
+        gu = self.linear(h, w_gate_up).float()
+        return (_act(gu[:, :intermediate], activation) * gu[:, intermediate:2 * intermediate]).to(self.dtype)
+
+    def rotate_norm_write(self, proj, q_col, k_col, v_col, heads, kv_heads, dim, vdim, inv_freq, rot_dims, value_eps,
+                          batch, cache):
+        rows = proj.shape[0]
+        pos = batch.row_pos.long()
+        half = rot_dims // 2
+
+        def rotate(x):
+            x = x.float()
+            if not half:
+                return x
+            a = pos.float()[:, None] * inv_freq.float()[None, :]
+            c, s = torch.cos(a)[:, None, :], torch.sin(a)[:, None, :]
+            u, v, rest = x[..., :half], x[..., half:rot_dims], x[..., rot_dims:]
+            return torch.cat([u * c - v * s, v * c + u * s, rest], dim=-1)
+
+        q = proj[:, q_col:q_col + heads * dim].view(rows, heads, dim)
+        q.copy_(rotate(q).to(proj.dtype))
+        k = rotate(proj[:, k_col:k_col + kv_heads * dim].reshape(rows, kv_heads, dim)).to(proj.dtype)
+        v = proj[:, v_col:v_col + kv_heads * vdim].reshape(rows, kv_heads, vdim).float()
+        if value_eps is not None:
+            v = v * torch.rsqrt((v * v).mean(dim=-1, keepdim=True) + value_eps)
+        slot = batch.seq_slot.long()[batch.row_seq.long()]
+        page = cache.table.long()[slot, (pos // PAGE) % cache.width]
+        cache.k[page, :, pos % PAGE] = k
+        cache.v[page, :, pos % PAGE] = v.to(proj.dtype)
+
+    def sink_attention(self, proj, q_col, heads, dim, vdim, sink, scale, window, batch, cache, out, out_col, out_scale):
+        rows = proj.shape[0]
+        G = heads // cache.kv_heads
+        q = proj[:, q_col:q_col + heads * dim].reshape(rows, heads, dim).float()
+        res = torch.empty((rows, heads, vdim), dtype=torch.float32, device=proj.device)
+        table = cache.table.long()
+        row0 = 0
+        for slot, start, n in zip(batch.slots, batch.starts, batch.q_lens):
+            total = start + n
+            lo = 0 if window is None else max(0, start - window + 1)
+            positions = torch.arange(lo, total, device=proj.device)
+            pages = table[slot, (positions // PAGE) % cache.width]
+            k = cache.k[pages, :, positions % PAGE].float()
+            v = cache.v[pages, :, positions % PAGE].float()
+            qpos = torch.arange(start, total, device=proj.device)
+            visible = positions[None, :] <= qpos[:, None]
+            if window is not None:
+                visible &= positions[None, :] > qpos[:, None] - window
+            for h in range(heads):
+                s = (q[row0:row0 + n, h] @ k[:, h // G].t()) * scale
+                s = s.masked_fill(~visible, float("-inf"))
+                m = s.max(dim=-1, keepdim=True).values
+                extra = 0.0
+                if sink is not None:
+                    m = torch.maximum(m, sink[h].float())
+                    extra = torch.exp(sink[h].float() - m)
+                p = torch.exp(s - m)
+                res[row0:row0 + n, h] = (p @ v[:, h // G]) / (p.sum(dim=-1, keepdim=True) + extra)
+            row0 += n
+        out[:, out_col:out_col + heads * vdim] = (res * out_scale).to(out.dtype).view(rows, heads * vdim)
+
+    def token_shift(self, h, last_state, mu, batch):
+        hf = h.float()
+        prev = torch.empty_like(hf)
+        prev[1:] = hf[:-1]
+        row0 = 0
+        for slot, n in zip(batch.slots, batch.q_lens):
+            prev[row0] = last_state[slot]
+            row0 += n
+        return (hf[None] + (prev - hf)[None] * mu.float()[:, None, :]).to(h.dtype)
+
+    def linear_recurrence(self, kind, r, k, v, gate, lora, w2, w0, heads, dim, norm_w, eps, state, batch, out, out_col,
+                          out_scale, rate=None, rate_bias=None, decay_scale=1.0, bonus=None, last_rows=None):
+        rows, H, N = r.shape[0], heads, dim
+        f = lambda t: t.float().reshape(rows, H, N)
+        z = torch.tanh(lora.float()).to(self.dtype).float() @ w2.float().t() + w0.float()
+        if kind == "delta":
+            decay = torch.exp(-decay_scale * torch.sigmoid(z)).view(rows, H, N)
+            a = torch.sigmoid(rate.float() + rate_bias.float()).view(rows, H, N)
+            g = torch.sigmoid(gate.float())
+        else:
+            decay = torch.exp(-torch.exp(z)).view(rows, H, N)
+            g = gate.float() * torch.sigmoid(gate.float())
+            bon = bonus.float().view(H, N)
+        rr, kk, vv = f(r), f(k), f(v)
+        o = torch.empty((rows, H, N), dtype=torch.float32, device=r.device)
+        row0 = 0
+        for slot, n in zip(batch.slots, batch.q_lens):
+            S = state[slot].clone()
+            for t in range(row0, row0 + n):
+                kv = kk[t][:, :, None] * vv[t][:, None, :]
+                if kind == "delta":
+                    u = kk[t] / torch.sqrt((kk[t] * kk[t]).sum(dim=-1, keepdim=True) + 1e-6)
+                    uS = torch.einsum("hi,hij->hj", u, S)
+                    S = decay[t][:, :, None] * S - (a[t] * u)[:, :, None] * uS[:, None, :] + kv
+                    o[t] = torch.einsum("hi,hij->hj", rr[t], S)
+                else:
+                    o[t] = torch.einsum("hi,hij->hj", rr[t], S + bon[:, :, None] * kv)
+                    S = decay[t][:, :, None] * S + kv
+            state[slot] = S
+            if last_rows is not None:
+                last_rows[1][slot] = last_rows[0][row0 + n - 1].float()
+            row0 += n
+        o = o * torch.rsqrt((o * o).mean(dim=-1, keepdim=True) + eps)
+        res = o.reshape(rows, H * N) * norm_w.float() * g * out_scale
+        out[:, out_col:out_col + H * N] = res.to(out.dtype)
+
+
+for _name, _fn in vars(_WideOps).items():
+    if not _name.startswith("__"):
+        setattr(TorchOps, _name, _fn)
