@@ -51,6 +51,20 @@ _SIGNATURES = {
     "krk_lt_gemm_bf16": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "krk_lt_gemm_report": [_P, _P],
 }
+_MIX_SIGNATURES = {
+    "krk_embed_scaled": [_P, _P, _P, c_int, c_int, c_int, c_float, _P, c_int, _P],
+    "krk_rmsnorm_wide": [_P, _P, _P, _P, _P, c_float, c_int, c_int, c_float, c_int, _P],
+    "krk_gated_act": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "krk_rotate_norm_write": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_float, _P, _P,
+                              _P, _P, c_int, _P, _P, c_int, c_int, _P],
+    "krk_sink_attention": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P,
+                           c_int, _P, _P, c_int, c_float, c_int, c_int, _P],
+    "krk_token_shift": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P],
+    "krk_linear_recurrence": [c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, _P, _P, _P, _P,
+                              _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int,
+                              c_int, _P, _P, _P, c_int, _P],
+}
+_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "sigmoid": 2}
 _ATTN_SIGNATURES = {
     "krk_attention_simple": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P],
     "krk_attention_head_dim": [],
@@ -97,6 +111,7 @@ class Kernels:
             raise KernelError("no CUDA device: this library computes with its CUDA kernels only")
         self.device = torch.device(device)
         self.core = _load(build_library("core"), _SIGNATURES)
+        self._mix = None
         self.attn: dict[int, ctypes.CDLL] = {}
         for d in head_dims:
             self._attn_lib(int(d))
@@ -427,6 +442,106 @@ class Kernels:
             buf = self._partials[key] = torch.empty(n_seqs * heads * splits * (head_dim + 2), dtype=torch.float32,
                                                     device=self.device)
         return splits, buf
+
+    # -- 32-bit residual stream, windowed attention with a sink, recurrent state -------------------
+    @property
+    def mix(self) -> ctypes.CDLL:
+        """The library of these kernels, compiled and loaded when a model first asks for one of them."""
+        if self._mix is None:
+            self._mix = _load(build_library("mix"), _MIX_SIGNATURES)
+        return self._mix
+
+    @staticmethod
+    def _rows_view(t):
+        """(pointer, row stride) of a 2-D view whose rows are contiguous."""
+        if t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError("a kernel input must be a 2-D tensor (or column slice) with contiguous rows")
+        return t.data_ptr(), t.stride(0)
+
+    def embed_scaled(self, table, tokens, n_rows, scale):
+        out = torch.empty((n_rows, table.shape[1]), dtype=torch.float32, device=table.device)
+        self._ok(self.mix.krk_embed_scaled(out.data_ptr(), table.data_ptr(), tokens.data_ptr(), n_rows, table.shape[1],
+                                           table.shape[0], float(scale), self.error.data_ptr(), _code(table.dtype),
+                                           self._stream()), "scaled embedding gather")
+        return out
+
+    def rmsnorm_wide(self, x, branch, gain, offset, eps, x_new, out_dtype):
+        """Rows of a float32 stream, normalised into ``out_dtype``; with a branch, ``x_new`` = x + branch (float32)."""
+        if x.dtype != torch.float32 or gain.dtype != torch.float32 or not x.is_contiguous():
+            raise KernelError("the wide norm reads a contiguous float32 stream and a float32 gain")
+        if branch is not None and (branch.dtype != out_dtype or not branch.is_contiguous() or branch.shape != x.shape):
+            raise KernelError("the wide norm's branch must have the path's dtype and the stream's shape")
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        self._ok(self.mix.krk_rmsnorm_wide(out.data_ptr(), x_new.data_ptr() if branch is not None else None, x.data_ptr(),
+                                           _ptr(branch), gain.data_ptr(), float(offset), x.shape[0], x.shape[1], float(eps),
+                                           _code(out_dtype), self._stream()), "wide rmsnorm")
+        return out
+
+    def gated_act(self, gu, intermediate, activation):
+        ptr, stride = self._rows_view(gu)
+        out = torch.empty((gu.shape[0], intermediate), dtype=gu.dtype, device=gu.device)
+        self._ok(self.mix.krk_gated_act(out.data_ptr(), ptr, stride, gu.shape[0], intermediate, _ACTIVATIONS[activation],
+                                        _code(gu.dtype), self._stream()), "gated activation")
+        return out
+
+    def gate_up_act(self, h, w_gate_up, intermediate, activation):
+        """act(gate h) * (up h) with W = cat(gate, up); silu on few bfloat16 rows runs in the product's epilogue."""
+        if activation == "silu" and self._use_skinny(h, w_gate_up):
+            return self.gate_up_swiglu(h, w_gate_up, intermediate)
+        return self.gated_act(self.linear(h, w_gate_up), intermediate, activation)
+
+    def rotate_norm_write(self, proj, q_col, k_col, v_col, heads, kv_heads, dim, vdim, inv_freq, rot_dims, value_eps,
+                          batch, cache):
+        """Rotate q in place, rotate k into the cache, write v (divided by its root mean square if
+        ``value_eps`` is a number) into the cache; columns are offsets into ``proj``'s rows."""
+        ptr, stride = self._rows_view(proj)
+        if cache.k.dtype != proj.dtype or cache.head_dim != dim or cache.v_dim != vdim or cache.kv_heads != kv_heads:
+            raise KernelError("the cache does not fit the heads it is to receive")
+        self._ok(self.mix.krk_rotate_norm_write(
+            ptr, stride, q_col, k_col, v_col, heads, kv_heads, dim, vdim, inv_freq.data_ptr(), rot_dims,
+            int(value_eps is not None), float(value_eps or 0.0), batch.row_seq.data_ptr(), batch.row_pos.data_ptr(),
+            batch.seq_slot.data_ptr(), cache.table.data_ptr(), cache.width, cache.k.data_ptr(), cache.v.data_ptr(),
+            proj.shape[0], _code(proj.dtype), self._stream()), "rotation + value norm + cache write")
+
+    def sink_attention(self, proj, q_col, heads, dim, vdim, sink, scale, window, batch, cache, out, out_col, out_scale):
+        ptr, stride = self._rows_view(proj)
+        optr, ostride = self._rows_view(out)
+        self._ok(self.mix.krk_sink_attention(
+            optr, ostride, out_col, float(out_scale), ptr, stride, q_col, heads, cache.kv_heads, dim, vdim, _ptr(sink),
+            batch.row_seq.data_ptr(), batch.row_pos.data_ptr(), batch.seq_slot.data_ptr(), cache.table.data_ptr(),
+            cache.width, cache.k.data_ptr(), cache.v.data_ptr(), proj.shape[0], float(scale), int(window or 0),
+            _code(proj.dtype), self._stream()), "windowed attention with a sink")
+
+    def token_shift(self, h, last_state, mu, batch):
+        """[mixes, rows, hidden]: h + (h_prev - h) * mu, the row before a step's first coming from ``last_state``."""
+        ptr, stride = self._rows_view(h)
+        rows, C = h.shape
+        out = torch.empty((mu.shape[0], rows, C), dtype=h.dtype, device=h.device)
+        self._ok(self.mix.krk_token_shift(out.data_ptr(), ptr, stride, last_state.data_ptr(), mu.data_ptr(), mu.shape[0],
+                                          C, rows, batch.row_seq.data_ptr(), batch.cu_q.data_ptr(),
+                                          batch.seq_slot.data_ptr(), _code(h.dtype), self._stream()), "token shift")
+        return out
+
+    def linear_recurrence(self, kind, r, k, v, gate, lora, w2, w0, heads, dim, norm_w, eps, state, batch, out, out_col,
+                          out_scale, rate=None, rate_bias=None, decay_scale=1.0, bonus=None, last_rows=None):
+        """The scan of a matrix-state mixer over a step's rows ("wkv" or "delta"); see csrc/recurrent.cu."""
+        views = [self._rows_view(t) for t in (r, k, v, gate)]
+        rate_v = self._rows_view(rate) if rate is not None else (None, 0)
+        lora_v = self._rows_view(lora)
+        optr, ostride = self._rows_view(out)
+        last_ptr, last_stride, C, last_state = None, 0, 0, None
+        if last_rows is not None:
+            (last_ptr, last_stride), C, last_state = self._rows_view(last_rows[0]), last_rows[0].shape[1], last_rows[1]
+        if state.dtype != torch.float32 or not state.is_contiguous() or not w2.is_contiguous() or w2.dtype != r.dtype:
+            raise KernelError("the recurrence keeps a contiguous float32 state and reads W2 in the path's dtype")
+        rc = self.mix.krk_linear_recurrence(
+            {"wkv": 0, "delta": 1}[kind], views[0][0], views[0][1], views[1][0], views[1][1], views[2][0], views[2][1],
+            views[3][0], views[3][1], rate_v[0], rate_v[1], lora_v[0], lora_v[1], w2.data_ptr(), w0.data_ptr(),
+            _ptr(rate_bias), _ptr(bonus), norm_w.data_ptr(), state.data_ptr(), last_ptr, last_stride, C,
+            _ptr(last_state), optr, ostride, out_col, float(out_scale), float(eps), float(decay_scale), heads, dim,
+            lora.shape[1], batch.n_seqs, batch.cu_q.data_ptr(), batch.seq_qlen.data_ptr(), batch.seq_slot.data_ptr(),
+            _code(r.dtype), self._stream())
+        self._ok(rc, f"{kind} recurrence (heads of up to 128 channels)")
 
     # -- token selection ------------------------------------------------------------
     def select_tokens(self, logits, temperature, seed, requests, step, feed=None, out=None):

@@ -1,8 +1,10 @@
 """Compiles this package's CUDA sources for sm_100a into shared libraries.
 
-Two kinds of library: ``core`` (kernels whose sizes are run-time arguments) and
+Three kinds of library: ``core`` (kernels whose sizes are run-time arguments),
 ``attn_d<D>`` (the attention kernels, compiled once per head size D with
-``-DKRK_HEAD_DIM=D``, so a model compiles only the head size it has). A library
+``-DKRK_HEAD_DIM=D``, so a model compiles only the head size it has) and ``mix``
+(the kernels of models with a 32-bit residual stream, windowed attention with a
+sink and recurrent state; loaded by the first model that has such a part). A library
 is rebuilt when a source or a flag changes (its name carries a hash of both) and
 is otherwise loaded as it is. Libraries live in ``csrc/_build`` inside the
 package when that is writable, else under ``$KRK_BUILD_DIR`` or a per-user
@@ -28,6 +30,7 @@ SRC_DIR = Path(__file__).parent
 
 CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_simple.cu", "select.cu", "skinny_bf16.cu", "gemm_tcgen05.cu", "lt_gemm.cu"]
 CORE_LIBS = ["-lcublasLt"]  # lt_gemm.cu; the process already holds the copy that torch loaded
+MIX_SOURCES = ["wide_rows.cu", "sink_attention.cu", "recurrent.cu"]
 ATTN_SOURCES = ["attention_simple.cu", "attention_mma.cu", "attention_tcgen05.cu"]
 HEADERS = ["common.cuh", "mma.cuh", "tcgen05.cuh", "attention_noalloc.h"]
 
@@ -76,18 +79,21 @@ def _existing(sources):
     return [s for s in sources if (SRC_DIR / s).is_file()]
 
 
-def _key(sources, defines) -> str:
+def _key(sources, defines, libs=None) -> str:
     h = hashlib.sha256()
     for name in list(sources) + _existing(HEADERS):
         h.update(name.encode())
         h.update((SRC_DIR / name).read_bytes())
-    h.update(" ".join(NVCC_FLAGS + list(defines) + CORE_LIBS).encode())
+    h.update(" ".join(NVCC_FLAGS + list(defines) + (list(libs) if libs is not None else CORE_LIBS)).encode())
     return h.hexdigest()[:12]
 
 
 def library_path(kind: str, head_dim: int | None = None) -> tuple[Path, list, list]:
     if kind == "core":
         sources, defines, stem = _existing(CORE_SOURCES), [], "libkrk_core"
+    elif kind == "mix":
+        sources, defines, stem = _existing(MIX_SOURCES), [], "libkrk_mix"
+        return build_dir() / f"{stem}_{_key(sources, defines, [])}.so", sources, defines
     else:
         sources, defines, stem = _existing(ATTN_SOURCES), [f"-DKRK_HEAD_DIM={int(head_dim)}"], f"libkrk_attn_d{int(head_dim)}"
     return build_dir() / f"{stem}_{_key(sources, defines)}.so", sources, defines
@@ -155,7 +161,7 @@ def build_library(kind: str, head_dim: int | None = None, verbose: bool = True) 
 
 def build_all(head_dims=(16, 32, 64, 128), verbose: bool = True) -> list[Path]:
     """Compile the core library and the attention library of every given head size."""
-    out = [build_library("core", verbose=verbose)]
+    out = [build_library("core", verbose=verbose), build_library("mix", verbose=verbose)]
     for d in head_dims:
         out.append(build_library("attn", d, verbose=verbose))
     return out

@@ -1,0 +1,108 @@
+// Row kernels of models whose residual stream is float32 on every path: a scaled
+// embedding gather, RMSNorm over a float32 stream with the residual add folded in,
+// and the gated activation of a feed-forward with the activation as an argument.
+//
+// Norm: s = x + branch (float32, written out as the new stream); y = s * rsqrt(mean(s^2)
+// + eps) * (offset + w), rounded once to the element type T of the path. The gain is
+// float32. One block per row, the row held in shared memory, global memory read once.
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void embed_scaled_kernel(float* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
+                                    int H, int n_table_rows, float scale, int* error) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int r = blockIdx.x;
+  const int id = ids[r];
+  const bool bad = id < 0 || id >= n_table_rows;
+  if (bad && threadIdx.x == 0 && error) atomicExch(error, 1);
+  const T* src = table + (size_t)(bad ? 0 : id) * H;
+  float* dst = out + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = bad ? 0.f : to_float<T>(src[i]) * scale;
+}
+
+template <typename T>
+__global__ void rmsnorm_wide_kernel(T* __restrict__ out, float* x_new, const float* x, const T* __restrict__ branch,
+                                    const float* __restrict__ gain, float offset, int H, float eps) {
+  extern __shared__ float row_s[];  // H floats
+  __shared__ float scratch[32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const size_t base = (size_t)blockIdx.x * H;
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float f = x[base + i];
+    if (branch) {
+      f += to_float<T>(branch[base + i]);
+      x_new[base + i] = f;
+    }
+    row_s[i] = f;
+    sq += f * f;
+  }
+  const float rstd = rsqrtf(block_sum(sq, scratch) / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[base + i] = from_float<T>(row_s[i] * rstd * (offset + gain[i]));
+}
+
+__device__ __forceinline__ float activation(float z, int act) {
+  if (act == 0) return z / (1.0f + expf(-z));                                                   // silu
+  if (act == 1) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));  // gelu, tanh form
+  return 1.0f / (1.0f + expf(-z));                                                              // sigmoid
+}
+
+// out[r, i] = round(act(g) * u), g = gu[r, i], u = gu[r, I + i]
+template <typename T>
+__global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, int gu_stride, int I, int act) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const size_t r = blockIdx.x;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
+    const float g = to_float<T>(gu[r * gu_stride + i]);
+    const float u = to_float<T>(gu[r * gu_stride + I + i]);
+    out[r * I + i] = from_float<T>(activation(g, act) * u);
+  }
+}
+
+}  // namespace
+
+KRK_API int krk_embed_scaled(float* out, const void* table, const int* ids, int rows, int H, int n_table_rows, float scale,
+                             int* error, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (dtype == KRK_DTYPE_F32)
+    return (int)launch_pdl(embed_scaled_kernel<float>, dim3(rows), dim3(128), 0, stream, out, (const float*)table, ids, H,
+                           n_table_rows, scale, error);
+  return (int)launch_pdl(embed_scaled_kernel<bf16>, dim3(rows), dim3(128), 0, stream, out, (const bf16*)table, ids, H,
+                         n_table_rows, scale, error);
+}
+
+template <typename T>
+static int launch_rmsnorm_wide(void* out, float* x_new, const float* x, const void* branch, const float* gain,
+                               float offset, int rows, int H, float eps, cudaStream_t stream) {
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 220 * 1024) return -2;
+  const int threads = H >= 4096 ? 1024 : (H >= 1024 ? 256 : 128);
+  auto kern = rmsnorm_wide_kernel<T>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return (int)launch_pdl(kern, dim3(rows), dim3(threads), smem, stream, (T*)out, x_new, x, (const T*)branch, gain, offset,
+                         H, eps);
+}
+
+KRK_API int krk_rmsnorm_wide(void* out, float* x_new, const float* x, const void* branch, const float* gain, float offset,
+                             int rows, int H, float eps, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  return dtype == KRK_DTYPE_F32 ? launch_rmsnorm_wide<float>(out, x_new, x, branch, gain, offset, rows, H, eps, stream)
+                                : launch_rmsnorm_wide<bf16>(out, x_new, x, branch, gain, offset, rows, H, eps, stream);
+}
+
+KRK_API int krk_gated_act(void* out, const void* gu, int gu_stride, int rows, int I, int act, int dtype,
+                          cudaStream_t stream) {
+  if (rows == 0) return 0;
+  const int chunks = min(64, (I + 255) / 256);
+  if (dtype == KRK_DTYPE_F32)
+    return (int)launch_pdl(gated_act_kernel<float>, dim3(rows, chunks), dim3(256), 0, stream, (float*)out,
+                           (const float*)gu, gu_stride, I, act);
+  return (int)launch_pdl(gated_act_kernel<bf16>, dim3(rows, chunks), dim3(256), 0, stream, (bf16*)out, (const bf16*)gu,
+                         gu_stride, I, act);
+}
