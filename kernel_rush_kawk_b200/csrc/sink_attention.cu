@@ -4,8 +4,10 @@
 // krk_rotate_norm_write: one warp per (row, head). A query head is rotated in place; a
 // key head is rotated and written to its page; a value head is (optionally) divided by
 // its root mean square and written to its page. Rotation: the first `rot` elements, element
-// i with element i + rot/2, by the angle position * inv_freq[i]; the product, sine and cosine
-// are float32 (sincosf, not the fast forms).
+// i with element i + rot/2, by the angle position * f_i. f_i arrives as two floats (its float32
+// value and the rest of its float64 value); the product's float32 value goes through sincosf (not
+// the fast forms) and the product's rounding error and the rest of f_i correct sine and cosine to
+// first order, so that an angle of a thousand radians is as exact as one of a few.
 //
 // krk_sink_attention: one warp per (row, head). The warp takes 32 keys at a time, one key
 // per lane: each lane's score is its own ordered sum over the head, the softmax runs online
@@ -18,6 +20,16 @@
 namespace {
 
 constexpr int MAX_V_PER_LANE = 8;  // value heads up to 256
+
+// sine and cosine of p * (f_hi + f_lo)
+__device__ __forceinline__ void angle_sincos(float p, float f_hi, float f_lo, float* s, float* c) {
+  const float a = __fmul_rn(p, f_hi);
+  const float e = fmaf(p, f_hi, -a) + p * f_lo;
+  float s0, c0;
+  sincosf(a, &s0, &c0);
+  *s = fmaf(e, c0, s0);
+  *c = fmaf(-e, s0, c0);
+}
 
 template <typename T>
 __global__ void rotate_norm_write_kernel(T* proj, int stride, int q_col, int k_col, int v_col, int HQ, int HKV, int D,
@@ -40,7 +52,7 @@ __global__ void rotate_norm_write_kernel(T* proj, int stride, int q_col, int k_c
     T* q = src + q_col + (size_t)which * D;
     for (int i = lane; i < half; i += 32) {
       float s, c;
-      sincosf(p * inv_freq[i], &s, &c);
+      angle_sincos(p, inv_freq[i], inv_freq[half + i], &s, &c);
       const float u = to_float<T>(q[i]), v = to_float<T>(q[i + half]);
       q[i] = from_float<T>(u * c - v * s);
       q[i + half] = from_float<T>(v * c + u * s);
@@ -55,7 +67,7 @@ __global__ void rotate_norm_write_kernel(T* proj, int stride, int q_col, int k_c
     T* dst = k_cache + (((size_t)page * HKV + h) * KRK_PAGE + (pos % KRK_PAGE)) * D;
     for (int i = lane; i < half; i += 32) {
       float s, c;
-      sincosf(p * inv_freq[i], &s, &c);
+      angle_sincos(p, inv_freq[i], inv_freq[half + i], &s, &c);
       const float u = to_float<T>(k[i]), v = to_float<T>(k[i + half]);
       dst[i] = from_float<T>(u * c - v * s);
       dst[i + half] = from_float<T>(v * c + u * s);

@@ -2,7 +2,7 @@
 
 q = Wq h, k = Wk h, v = Wv h (no biases); the first ``rot_dims`` elements of every
 q and k head are rotated by the position (element i with element i + rot_dims/2,
-angle p * rot_base^(-2i/rot_dims), positions and angles in 32-bit); with
+angle p * rot_base^(-2i/rot_dims), positions and angles in 32-bit or better); with
 ``value_norm`` every value head is divided by its root mean square before it is
 cached; a query at position p sees keys p - window + 1 .. p (``window`` None: all
 of 0..p); score = (q . k) * scale with ``scale`` a parameter; with ``sink`` each
@@ -59,8 +59,11 @@ class SinkWindowAttention(Branch):
         self.w = {k: tensors[k] for k in ("q", "k", "v", "o")}
         self.sink = tensors["sink"].float().contiguous() if self.has_sink else None
         # the few rotation frequencies come from the host in 64-bit, so that they depend on no device's pow()
+        # and as two floats each (the float32 value, then what float32 leaves of the float64 value)
         i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
-        self.inv_freq = (self.rot_base ** (-2.0 * i / max(self.rot_dims, 1))).to(torch.float32).to(runtime.device)
+        f = self.rot_base ** (-2.0 * i / max(self.rot_dims, 1))
+        hi = f.to(torch.float32)
+        self.inv_freq = torch.cat([hi, (f - hi.double()).to(torch.float32)]).contiguous().to(runtime.device)
         self.bind_standalone()
 
     def in_weight(self):

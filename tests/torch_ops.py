@@ -195,8 +195,9 @@ class _WideOps:
             x = x.float()
             if not half:
                 return x
-            a = pos.float()[:, None] * inv_freq.float()[None, :]
-            c, s = torch.cos(a)[:, None, :], torch.sin(a)[:, None, :]
+            f = inv_freq[:half].double() + inv_freq[half:].double()  # the frequencies come as two floats each
+            a = pos.double()[:, None] * f[None, :]
+            c, s = torch.cos(a).float()[:, None, :], torch.sin(a).float()[:, None, :]
             u, v, rest = x[..., :half], x[..., half:rot_dims], x[..., rot_dims:]
             return torch.cat([u * c - v * s, v * c + u * s, rest], dim=-1)
 
