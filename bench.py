@@ -21,6 +21,11 @@ at batch 1 and 64 (``points``); a 2,048-token prompt is prefilled (``prefill``).
   against the measured copy bandwidth.
 * ``prefill.frac``: the step's flops over its time over the measured bfloat16 peak.
 
+``--only design_taredra`` measures the Taredra hybrid decoder (windowed attention with a sink beside a
+delta rule, RWKV-style time mixing, a 32-bit residual stream) at two layer sizes beside the Qwen3 decoder of
+equal width, feed-forward, head and layer counts: prefill of 2,048 tokens and decode at batch 1 and 8 after
+1,024-token prompts, each with the time per family of kernels, and prints a line of its own.
+
 ``--only workload_8b`` and ``--only workload_14b`` run the baseline's two larger
 configurations (Qwen3-8B sizes: 8 prompts of 256 to 2,048 tokens, 128 greedy steps;
 Qwen3-14B sizes: 16 prompts of 512 to 4,096 tokens, 128 steps at temperature 0.7)
@@ -184,6 +189,130 @@ def run_workload(args) -> dict:
             "prompts": n, "prompt_tokens": st.prompt_tokens, "steps": produced, "temperature": temperature,
             "prefill_ms": round(st.prefill_ms, 2), "prefill_tokens_per_s": round(st.prefill_tokens_per_s, 1),
             "decode_ms_per_step": round(st.decode_ms_per_step, 4), "decode_tokens_per_s": round(st.decode_tokens_per_s, 1)}
+
+
+DESIGN_SIZES = {
+    # Taredra preset -> the Qwen3 decoder of equal width, feed-forward, heads and layers
+    "taredra_1b": {"hidden_size": 1536, "intermediate_size": 6144, "num_attention_heads": 12, "num_key_value_heads": 4,
+                   "head_dim": 128, "vocab_size": 32768},
+    "taredra_4b": {"hidden_size": 2560, "intermediate_size": 9728, "num_attention_heads": 32, "num_key_value_heads": 8,
+                   "head_dim": 128, "vocab_size": 151936},
+}
+KERNEL_FAMILIES = {
+    "product": ("_skinny", "_library_gemm", "_gemm_nt", "gemm_tcgen05"),
+    "norm": ("rmsnorm", "add_rmsnorm", "rmsnorm_wide"),
+    "activation": ("swiglu", "gated_act"),
+    "attention": ("rope_attention", "rotate_norm_write", "sink_attention"),
+    "recurrence": ("token_shift", "linear_recurrence"),
+    "embedding": ("embed", "embed_scaled", "gather_rows"),
+}
+
+
+def run_designs(args) -> dict:
+    """Taredra beside the Qwen3 decoder of equal size; see the module text."""
+    import torch
+
+    from kernel_rush_kawk_b200 import Engine, Qwen3Config, StepEntry
+    from kernel_rush_kawk_b200.config.registry import preset_config
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    gen = torch.Generator().manual_seed(99)
+    out = {"only": args.only, "prompt": PROMPT, "prefill_tokens": PREFILL_TOKENS, "sizes": {}, "peaks": pk}
+
+    def measure(cfg, vocab):
+        engine = Engine.from_random(cfg, seed=0, std=0.02, dtype="bfloat16", max_tokens=16 * CONTEXT, max_slots=16,
+                                    max_context=CONTEXT)
+        ops, cache, stepper = engine.ops, engine.cache, engine.stepper
+        res = {}
+        prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+
+        def prefill_once():
+            slot = cache.alloc()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            engine.step([StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            cache.free(slot)
+            return start.elapsed_time(end)
+
+        times = [prefill_once() for _ in range(args.warmup + 7)][args.warmup:]
+        res["prefill_ms"] = round(statistics.median(times), 3)
+        res["prefill_tokens_per_s"] = round(PREFILL_TOKENS * 1000.0 / statistics.median(times), 1)
+        for batch in (1, 8):
+            slots = [cache.alloc() for _ in range(batch)]
+            prompts = torch.randint(0, vocab, (batch, PROMPT), generator=gen).tolist()
+            logits = engine.step([StepEntry(s, p, [PROMPT - 1]) for s, p in zip(slots, prompts)])
+            first = stepper.decode_on_device(slots, logits.argmax(dim=-1).tolist(), args.warmup)[-1].tolist()
+            torch.cuda.synchronize()
+            runs = []
+            for _ in range(3):
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                first = stepper.decode_on_device(slots, first, args.steps)[-1].tolist()
+                end.record()
+                torch.cuda.synchronize()
+                runs.append(start.elapsed_time(end) / args.steps)
+            res[f"decode_b{batch}_ms"] = round(statistics.median(runs), 4)
+            res[f"decode_b{batch}_tokens_per_s"] = round(batch * 1000.0 / statistics.median(runs), 1)
+            res[f"decode_b{batch}_launches"] = stepper.graph_launches.get(batch, 0)
+            for s in slots:
+                cache.free(s)
+        # time per family of kernels: every leaf call between two events, kernel by kernel (no graph)
+        spent: dict = {}
+        wrapped = []
+        for family, names in KERNEL_FAMILIES.items():
+            for name in names:
+                fn = getattr(ops, name, None)
+                if fn is None:
+                    continue
+
+                def timed(*a, _fn=fn, _family=family, **k):
+                    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    start.record()
+                    r = _fn(*a, **k)
+                    end.record()
+                    spent.setdefault(_family, []).append((start, end))
+                    return r
+
+                setattr(ops, name, timed)
+                wrapped.append(name)
+        try:
+            def collect():
+                torch.cuda.synchronize()
+                got = {f: round(sum(a.elapsed_time(b) for a, b in pairs), 3) for f, pairs in spent.items()}
+                spent.clear()
+                return got
+
+            prefill_once()
+            collect()
+            prefill_once()
+            res["prefill_ms_by_family"] = collect()
+            stepper.use_graphs = False
+            slots = [cache.alloc() for _ in range(8)]
+            prompts = torch.randint(0, vocab, (8, PROMPT), generator=gen).tolist()
+            engine.step([StepEntry(s, p, []) for s, p in zip(slots, prompts)])
+            engine.step([StepEntry(s, [1], [0]) for s in slots])
+            collect()
+            engine.step([StepEntry(s, [2], [0]) for s in slots])
+            res["decode_b8_ms_by_family"] = collect()
+        finally:
+            for name in wrapped:
+                delattr(ops, name)
+        del engine
+        torch.cuda.empty_cache()
+        return res
+
+    for preset, twin in DESIGN_SIZES.items():
+        t_cfg = preset_config(preset)
+        layers = args.layers or len(t_cfg.layers)
+        t_cfg = type(t_cfg).from_dict({**t_cfg.to_dict(), "layers": t_cfg.to_dict()["layers"][:layers]})
+        q_cfg = Qwen3Config.from_dict({**twin, "num_hidden_layers": layers, "rms_norm_eps": 1e-6, "rope_theta": 1e4,
+                                       "tie_word_embeddings": True, "max_position_embeddings": CONTEXT})
+        out["sizes"][preset] = {"layers": layers, "taredra": measure(t_cfg, t_cfg.vocab),
+                                "qwen3": measure(q_cfg, q_cfg.vocab_size)}
+    return out
 
 
 def run_ours(args) -> dict:
@@ -492,7 +621,7 @@ def main() -> int:
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--only", default="", choices=["", "prefill", "decode_b1", "decode_b8", "decode_b16", "decode_b32", "decode_b64",
-                                                  "workload_8b", "workload_14b"],
+                                                  "workload_8b", "workload_14b", "design_taredra"],
                    help="run one piece only (for profiling), or one of the baseline's larger configurations end to end")
     p.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (both numbers are reported)")
     args = p.parse_args()
@@ -504,6 +633,9 @@ def main() -> int:
         print(f"bench.py runs on one GPU only (this library has no multi-GPU path); got --gpus {args.gpus}")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.only == "design_taredra":
+        print(json.dumps(run_designs(args)))
+        return 0
     print(json.dumps(run_workload(args) if args.only in WORKLOADS else run_ours(args)))
     return 0
 

@@ -117,6 +117,35 @@ __device__ __forceinline__ void pv_tile(float (&o)[DTILES][4], const float (&p)[
   }
 }
 
+// The same with the probabilities kept to about 16 bits of mantissa: p = hi + lo with both halves bfloat16, two
+// MMAs per fragment of V. For models whose softmax weights are 32-bit quantities: what is lost is below
+// 2^-16 of a weight, the order of the float32 exponential's own error.
+template <int NTILES>
+__device__ __forceinline__ void pv_tile_wide(float (&o)[DTILES][4], const float (&p)[NTILES][4], const bf16* vs, int key0,
+                                             int lane) {
+#pragma unroll
+  for (int kk = 0; kk < NTILES / 2; ++kk) {
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int f = 0; f < 4; ++f) {
+      const float x = p[2 * kk + (f >> 1)][2 * (f & 1)], y = p[2 * kk + (f >> 1)][2 * (f & 1) + 1];
+      const float xh = __bfloat162float(__float2bfloat16_rn(x)), yh = __bfloat162float(__float2bfloat16_rn(y));
+      hi[f] = pack_bf16x2(xh, yh);
+      lo[f] = pack_bf16x2(x - xh, y - yh);
+    }
+#pragma unroll
+    for (int n = 0; n < DTILES; n += 2) {
+      uint32_t b0, b1, b2, b3;
+      const bf16* q = vs + page_off<false>(key0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, n + (lane >> 4));
+      ldmatrix_x4_trans(b0, b1, b2, b3, q);
+      mma_bf16_16816(o[n], hi[0], hi[1], hi[2], hi[3], b0, b1);
+      mma_bf16_16816(o[n], lo[0], lo[1], lo[2], lo[3], b0, b1);
+      mma_bf16_16816(o[n + 1], hi[0], hi[1], hi[2], hi[3], b2, b3);
+      mma_bf16_16816(o[n + 1], lo[0], lo[1], lo[2], lo[3], b2, b3);
+    }
+  }
+}
+
 // Load the A fragments of one 16-row tile of queries; row r of the tile is at qrow[r half] (null: zero row).
 __device__ __forceinline__ void load_q(uint32_t (&qf)[KSTEPS][4], const bf16* q_lo, const bf16* q_hi, int lane) {
   const int t = lane & 3;
@@ -280,6 +309,114 @@ attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ qkv, i
   for (int h = 0; h < 2; ++h) {
     if (!op[h]) continue;
     const float inv = 1.0f / l[h];
+#pragma unroll
+    for (int n = 0; n < DTILES; ++n)
+      *reinterpret_cast<uint32_t*>(op[h] + n * 8 + 2 * t4) = pack_bf16x2(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// The same walk for windowed attention with a softmax sink: every row starts from (maximum = its head's
+// sink, sum = 1, no value) instead of (-inf, 0); the weights reach P.V as two bfloat16 halves; queries are
+// read from, and outputs written into, column ranges of wider rows, the output multiplied by out_scale.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS)
+sink_window_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_scale, const bf16* __restrict__ q_base,
+                           int q_stride, int HQ, int HKV, const float* __restrict__ sink,
+                           const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                           const int* __restrict__ seq_qlen, const int* __restrict__ cu_q, const int* __restrict__ table,
+                           int width, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                           float scale_log2, int window) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* smem = reinterpret_cast<bf16*>(smem_raw);  // [2 stages][K, V][64][KVP]
+  const int seq = blockIdx.z, kh = blockIdx.y;
+  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int G = HQ / HKV;
+  const int q_len = seq_qlen[seq];
+  const int n_rows = q_len * G;
+  if (tile * 64 >= n_rows) return;
+  const int start = seq_start[seq], slot = seq_slot[seq], row0 = cu_q[seq];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+
+  int pos[2], lo[2];
+  const bf16* qp[2];
+  bf16* op[2];
+  float m[2], l[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int R = tile * 64 + warp * 16 + g + 8 * h;
+    const bool ok = R < n_rows;
+    const int tok = ok ? R / G : -1;
+    const int head = kh * G + (ok ? R % G : 0);
+    pos[h] = ok ? start + tok : -1;
+    lo[h] = (ok && window > 0) ? max(0, pos[h] - window + 1) : 0;
+    qp[h] = ok ? q_base + (size_t)(row0 + tok) * q_stride + (size_t)head * D : nullptr;
+    op[h] = ok ? out + (size_t)(row0 + tok) * out_stride + (size_t)head * D : nullptr;
+    m[h] = sink ? sink[head] * LOG2E : -INFINITY;
+    l[h] = sink ? 1.f : 0.f;
+  }
+  uint32_t qf[KSTEPS][4];
+  load_q(qf, qp[0], qp[1], lane);
+  int warp_min_pos = min(pos[0], pos[1]), warp_max_lo = max(lo[0], lo[1]);
+#pragma unroll
+  for (int o2 = 16; o2 > 0; o2 >>= 1) {
+    warp_min_pos = min(warp_min_pos, __shfl_xor_sync(0xffffffffu, warp_min_pos, o2));
+    warp_max_lo = max(warp_max_lo, __shfl_xor_sync(0xffffffffu, warp_max_lo, o2));
+  }
+  const int last_tok = min(q_len - 1, (tile * 64 + 63) / G);
+  const int first_tok = (tile * 64) / G;
+  const int j_hi = (start + last_tok) / KRK_PAGE;
+  const int j_lo = window > 0 ? max(0, start + first_tok - window + 1) / KRK_PAGE : 0;
+  const size_t page_stride = (size_t)HKV * KRK_PAGE * D;
+  const size_t head_off = (size_t)kh * KRK_PAGE * D;
+
+  auto issue = [&](int j, int stage) {
+    const int page = table[(size_t)slot * width + j % width];
+    bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
+    load_page(ks, k_cache + (size_t)page * page_stride + head_off);
+    load_page(ks + TILE_ELEMS, v_cache + (size_t)page * page_stride + head_off);
+    cp_async_commit();
+  };
+
+  float o[DTILES][4];
+#pragma unroll
+  for (int n = 0; n < DTILES; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+
+  issue(j_lo, 0);
+  for (int j = j_lo; j <= j_hi; ++j) {
+    const int stage = (j - j_lo) & 1;
+    if (j + 1 <= j_hi) {
+      issue(j + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
+    const bf16* vs = ks + TILE_ELEMS;
+    float s[8][4];
+    qk_tile<8>(s, qf, ks, 0, lane);
+    const int key_base = j * KRK_PAGE;
+    const bool whole = key_base + KRK_PAGE - 1 <= warp_min_pos && key_base >= warp_max_lo;
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = key_base + n * 8 + 2 * t4 + (c & 1);
+        const int h = c >> 1;
+        s[n][c] = (whole || (key <= pos[h] && key >= lo[h])) ? s[n][c] * scale_log2 : -INFINITY;
+      }
+    softmax_update<8>(s, m, l, o);
+    pv_tile_wide<8>(o, s, vs, 0, lane);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (!op[h]) continue;
+    const float inv = out_scale / l[h];
 #pragma unroll
     for (int n = 0; n < DTILES; ++n)
       *reinterpret_cast<uint32_t*>(op[h] + n * 8 + 2 * t4) = pack_bf16x2(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
@@ -1233,6 +1370,31 @@ KRK_API int krk_attention_prefill(void* out, const void* qkv, int q_stride, int 
   attention_prefill_kernel<<<grid, THREADS, PAGE_SMEM, stream>>>(
       (bf16*)out, (const bf16*)qkv, q_stride, HQ, HKV, seq_slot, seq_start, seq_qlen, cu_q, table, width,
       (const bf16*)k_cache, (const bf16*)v_cache, scale * LOG2E, window);
+  KRK_CHECK_LAUNCH();
+  return 0;
+}
+
+// Windowed attention with a sink for steps of many tokens. q_base and out point at the first query / output
+// column of the wider rows (strides in elements; both even, as are the column offsets).
+KRK_API int krk_sink_window_prefill(void* out, int out_stride, float out_scale, const void* q_base, int q_stride, int HQ,
+                                    int HKV, const float* sink, const int* seq_slot, const int* seq_start,
+                                    const int* seq_qlen, const int* cu_q, const int* table, int width,
+                                    const void* k_cache, const void* v_cache, int n_seqs, int max_q_len, float scale,
+                                    int window, cudaStream_t stream) {
+  if (n_seqs == 0 || max_q_len == 0) return 0;
+  const int G = HQ / HKV;
+  const long long tiles = ((long long)max_q_len * G + 63) / 64;
+  if (tiles > 0x7fffffffLL || HKV > 65535 || n_seqs > 65535) return -3;
+  if ((out_stride & 1) || (q_stride & 1) || ((uintptr_t)out & 3) || ((uintptr_t)q_base & 3)) return -2;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(sink_window_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAGE_SMEM);
+    configured = true;
+  }
+  dim3 grid((unsigned)tiles, HKV, n_seqs);
+  sink_window_prefill_kernel<<<grid, THREADS, PAGE_SMEM, stream>>>(
+      (bf16*)out, out_stride, out_scale, (const bf16*)q_base, q_stride, HQ, HKV, sink, seq_slot, seq_start, seq_qlen,
+      cu_q, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale * LOG2E, window);
   KRK_CHECK_LAUNCH();
   return 0;
 }

@@ -59,6 +59,8 @@ _MIX_SIGNATURES = {
                               _P, _P, c_int, _P, _P, c_int, c_int, _P],
     "krk_sink_attention": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P,
                            c_int, _P, _P, c_int, c_float, c_int, c_int, _P],
+    "krk_sink_attention_single": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
+                                  c_int, _P, _P, c_int, c_float, c_int, c_int, _P],
     "krk_token_shift": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P],
     "krk_linear_recurrence": [c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, _P, _P, _P, _P,
                               _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int,
@@ -70,6 +72,8 @@ _ATTN_SIGNATURES = {
     "krk_attention_head_dim": [],
     "krk_attention_prefill": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_float,
                               c_int, _P],
+    "krk_sink_window_prefill": [_P, c_int, c_float, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int,
+                                c_int, c_float, c_int, _P],
     "krk_attention_decode": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P,
                              _P],
     "krk_attention_prefill_tcgen05": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int,
@@ -506,6 +510,29 @@ class Kernels:
     def sink_attention(self, proj, q_col, heads, dim, vdim, sink, scale, window, batch, cache, out, out_col, out_scale):
         ptr, stride = self._rows_view(proj)
         optr, ostride = self._rows_view(out)
+        if batch.is_decode and proj.shape[0] == batch.n_seqs:
+            # one token per sequence: a block per (sequence, kv head), its warps splitting the window's keys. The
+            # choice depends on the step's shape alone, so a sequence's results do not depend on its batch
+            rc = self.mix.krk_sink_attention_single(
+                optr, ostride, out_col, float(out_scale), ptr, stride, q_col, heads, cache.kv_heads, dim, vdim,
+                _ptr(sink), batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), cache.table.data_ptr(), cache.width,
+                cache.k.data_ptr(), cache.v.data_ptr(), batch.n_seqs, float(scale), int(window or 0), _code(proj.dtype),
+                self._stream())
+            if rc != -2:  # -2: heads too large for it; the general kernel takes them
+                self._ok(rc, "single-token windowed attention with a sink")
+                return
+        if (proj.dtype == torch.bfloat16 and dim == vdim and dim % 16 == 0 and dim <= 256 and dim in self.attn
+                and not batch.is_decode and hasattr(self.attn[dim], "krk_sink_window_prefill")):
+            # many tokens per sequence in bfloat16: the tensor-core walk over whole pages (compiled per head size)
+            esz = proj.element_size()
+            rc = self.attn[dim].krk_sink_window_prefill(
+                optr + out_col * esz, ostride, float(out_scale), ptr + q_col * esz, stride, heads, cache.kv_heads,
+                _ptr(sink), batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), batch.seq_qlen.data_ptr(),
+                batch.cu_q.data_ptr(), cache.table.data_ptr(), cache.width, cache.k.data_ptr(), cache.v.data_ptr(),
+                batch.n_seqs, batch.max_q_len, float(scale), int(window or 0), self._stream())
+            if rc != -2:  # -2: odd strides or offsets; the general kernel takes them
+                self._ok(rc, "tensor-core windowed attention with a sink")
+                return
         self._ok(self.mix.krk_sink_attention(
             optr, ostride, out_col, float(out_scale), ptr, stride, q_col, heads, cache.kv_heads, dim, vdim, _ptr(sink),
             batch.row_seq.data_ptr(), batch.row_pos.data_ptr(), batch.seq_slot.data_ptr(), cache.table.data_ptr(),

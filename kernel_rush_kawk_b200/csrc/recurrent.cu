@@ -11,12 +11,13 @@
 //   a = sigmoid(rate + rate_bias)
 //   out = o / sqrt(mean_head(o^2) + eps) * norm_w * gate(g) * out_scale, gate = silu (rule 0) or sigmoid (rule 1)
 //
-// One block per (sequence, head); thread j owns column j of S in registers for the whole pass, so
-// the sums over key channels are private, ordered sums and the token loop has no barrier. Tokens
-// are taken in chunks: the block first computes the chunk's decays, unit keys and rates in
-// parallel into shared memory (float32), then every thread walks the chunk's tokens alone, then
-// the block normalises and gates the chunk's outputs in parallel. A token's result is the same
-// to the bit however the sequence was cut into steps: the chunking regroups work, not sums.
+// One block per (sequence, head). Column j of S (all key channels of one value channel) is spread over
+// KL adjacent lanes, 16 or 32 key channels each, in registers for the whole pass; a sum over key channels
+// is each lane's ordered partial sum followed by a fixed exchange between the KL lanes, and the token
+// loop has no block-wide barrier. Tokens are taken in chunks, and the block is two groups of threads:
+// while one scans a chunk, the other computes the next chunk's decays, unit keys and rates into shared
+// memory (float32) and normalises, gates and stores the chunk before. A token's result is the same to
+// the bit however the sequence was cut into steps: the chunking regroups work, not sums.
 #include "common.cuh"
 
 namespace {
@@ -60,43 +61,82 @@ struct ScanArgs {
   float out_scale, eps, decay_scale;
   int H, N, R, n_seqs;
   const int *cu_q, *seq_qlen, *seq_slot;
+  int vec;  // rows, strides and the head size allow accesses of four elements at a time
 };
+
+template <typename T> __device__ __forceinline__ void load4_el(const T* p, float* f);
+template <> __device__ __forceinline__ void load4_el<float>(const float* p, float* f) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4_el<bf16>(const bf16* p, float* f) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  f[0] = __low2float(h[0]); f[1] = __high2float(h[0]); f[2] = __low2float(h[1]); f[3] = __high2float(h[1]);
+}
+template <typename T> __device__ __forceinline__ void store4_el(T* p, const float* f);
+template <> __device__ __forceinline__ void store4_el<float>(float* p, const float* f) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+template <> __device__ __forceinline__ void store4_el<bf16>(bf16* p, const float* f) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned*>(&a);
+  raw.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
 
 __device__ __forceinline__ float sigmoidf(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-template <typename T, int RULE, int NCAP, int TC>
-__global__ void __launch_bounds__(NCAP) recurrence_kernel(ScanArgs a) {
-  extern __shared__ float sm[];
+constexpr int PROD = 128;  // threads that prepare and finish chunks beside the threads that scan
+
+__device__ __forceinline__ void producers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(PROD) : "memory"); }
+
+// NPT: key channels of a column that one lane keeps (16 for heads of up to 64 channels, 32 up to 128).
+// A lane's slice of a staged vector starts NPT + 4 floats after its neighbour's, so that the four
+// slices a quarter-warp reads at once fall into different banks. TC: tokens per chunk.
+//
+// The block's first `cons` threads scan; its last PROD threads prepare the chunk after the one being
+// scanned (stage r, k, v; unit-key norms; decays and rates) into the other of two buffers and finish the
+// chunk before it (per-head norm, weight, gate, store). The two groups meet once per chunk.
+template <typename T, int RULE, int NPT, int TC, int MAXT>
+__global__ void __launch_bounds__(MAXT, 1) recurrence_kernel(ScanArgs a, int KL, int cons) {
+  constexpr int SL = NPT + 4;
+  extern __shared__ __align__(16) float sm[];
   const int N = a.N, R = a.R;
-  float* r_s = sm;                 // [TC][N]
-  float* k_s = r_s + TC * N;       // [TC][N]
-  float* v_s = k_s + TC * N;       // [TC][N]
-  float* w_s = v_s + TC * N;       // [TC][N] decay
-  float* u_s = w_s + TC * N;       // [TC][N] unit key (rule 1) / bonus * k (rule 0)
-  float* au_s = u_s + TC * N;      // [TC][N] rate * unit key (rule 1)
-  float* o_s = au_s + TC * N;      // [TC][N]
-  float* w2_s = o_s + TC * N;      // [R][N]
-  float* th_s = w2_s + R * N;      // [TC][R] tanh of the low-rank input
-  float* red_s = th_s + TC * R;    // [TC] per-token reductions
+  const int VS = KL * SL;            // floats of one staged vector of one token
+  const int BUF = 5 * TC * VS + TC * N;  // r, k, decay, u, au (padded slices), then v [TC][N]
+  float* o_s = sm + 2 * BUF;         // [2][TC][N]
+  float* w2_s = o_s + 2 * TC * N;    // [R][N]
+  float* th_s = w2_s + R * N;        // [TC][R] tanh of the low-rank input
+  float* red_s = th_s + TC * R;      // [2][TC] per-token reductions of the producers
 
   grid_launch_dependents();
   const int seq = blockIdx.x / a.H, head = blockIdx.x % a.H;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+  const int tid = threadIdx.x;
   const int ch0 = head * N;
-  // weights first: no kernel writes them
+  // weights first (no kernel writes them), and zeros where a slice reaches past the head's channels
   for (int i = tid; i < R * N; i += blockDim.x) {
     const int m = i / N, c = i % N;
     w2_s[i] = to_float<T>(reinterpret_cast<const T*>(a.w2)[(size_t)(ch0 + c) * R + m]);
   }
+  for (int i = tid; i < 2 * BUF; i += blockDim.x) sm[i] = 0.f;
   grid_dependency_wait();
   const int row0 = a.cu_q[seq], T_len = a.seq_qlen[seq], slot = a.seq_slot[seq];
-  const bool on = tid < N;
-
-  float S[NCAP];
+  const int n_chunks = (T_len + TC - 1) / TC;
+  const bool consumer = tid < cons;
   float* st = a.state + (((size_t)slot * a.H + head) * N) * N;
-#pragma unroll
-  for (int i = 0; i < NCAP; ++i) S[i] = (on && i < N) ? st[(size_t)i * N + tid] : 0.f;
 
+  // consumer: value channel `col`, key channels key0 .. key0 + NPT - 1
+  const int col = tid / KL, slice = tid % KL;
+  const bool on = consumer && col < N;
+  const int key0 = slice * NPT;
+  float S[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) S[i] = (on && key0 + i < N) ? st[(size_t)(key0 + i) * N + col] : 0.f;
+
+  // producer
+  const int pt = tid - cons, plane = pt & 31, pwarp = pt >> 5;
   const T* rp = reinterpret_cast<const T*>(a.r);
   const T* kp = reinterpret_cast<const T*>(a.k);
   const T* vp = reinterpret_cast<const T*>(a.v);
@@ -104,138 +144,229 @@ __global__ void __launch_bounds__(NCAP) recurrence_kernel(ScanArgs a) {
   const T* ap = reinterpret_cast<const T*>(a.rate);
   const T* lp = reinterpret_cast<const T*>(a.lora);
   T* outp = reinterpret_cast<T*>(a.out);
+  __syncthreads();
 
-  for (int t0 = 0; t0 < T_len; t0 += TC) {
-    const int nt = min(TC, T_len - t0);
-    __syncthreads();  // the chunk before is out of shared memory
-    // -- stage r, k, v and the tanh of the low-rank input ------------------------------------
-    for (int i = tid; i < nt * N; i += blockDim.x) {
-      const int t = i / N, c = i % N;
-      const size_t row = (size_t)(row0 + t0 + t);
-      r_s[i] = to_float<T>(rp[row * a.r_stride + ch0 + c]);
-      k_s[i] = to_float<T>(kp[row * a.k_stride + ch0 + c]);
-      v_s[i] = to_float<T>(vp[row * a.v_stride + ch0 + c]);
-    }
-    for (int i = tid; i < nt * R; i += blockDim.x) {
-      const int t = i / R, m = i % R;
-      th_s[i] = round_to<T>(tanhf(to_float<T>(lp[(size_t)(row0 + t0 + t) * a.lora_stride + m])));
-    }
-    __syncthreads();
-    // -- per token: sum of squared key channels (rule 1) ---------------------------------------
-    if (RULE == 1) {
-      for (int t = warp; t < nt; t += n_warps) {
-        float sq = 0.f;
-        for (int c = lane; c < N; c += 32) sq += k_s[t * N + c] * k_s[t * N + c];
-        sq = warp_sum(sq);
-        if (lane == 0) red_s[t] = rsqrtf(sq + 1e-6f);
+  for (int c = 0; c < n_chunks + 2; ++c) {
+    if (consumer) {
+      const int cc = c - 1;  // the chunk to scan
+      if (cc >= 0 && cc < n_chunks) {
+        const int nt = min(TC, T_len - cc * TC);
+        const float* buf = sm + (cc & 1) * BUF;
+        const float* v_s = buf + 5 * TC * VS;
+        float* o_c = o_s + (cc & 1) * TC * N;
+        for (int t = 0; t < nt; ++t) {
+          const int at = t * VS + slice * SL;
+          const float4* r4 = reinterpret_cast<const float4*>(buf + at);
+          const float4* k4 = reinterpret_cast<const float4*>(buf + TC * VS + at);
+          const float4* w4 = reinterpret_cast<const float4*>(buf + 2 * TC * VS + at);
+          const float4* u4 = reinterpret_cast<const float4*>(buf + 3 * TC * VS + at);
+          const float vj = on ? v_s[t * N + col] : 0.f;
+          float o0 = 0.f, o1 = 0.f;
+          if (RULE == 1) {
+            const float4* a4 = reinterpret_cast<const float4*>(buf + 4 * TC * VS + at);
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int q = 0; q < NPT / 4; ++q) {
+              const float4 u = u4[q];
+              s0 += u.x * S[4 * q];
+              s1 += u.y * S[4 * q + 1];
+              s0 += u.z * S[4 * q + 2];
+              s1 += u.w * S[4 * q + 3];
+            }
+            float uS = s0 + s1;
+            for (int off = 1; off < KL; off <<= 1) uS += __shfl_xor_sync(0xffffffffu, uS, off);
+#pragma unroll
+            for (int q = 0; q < NPT / 4; ++q) {
+              const float4 w = w4[q], au = a4[q], k = k4[q], r = r4[q];
+              S[4 * q] = w.x * S[4 * q] - au.x * uS + k.x * vj;
+              o0 += r.x * S[4 * q];
+              S[4 * q + 1] = w.y * S[4 * q + 1] - au.y * uS + k.y * vj;
+              o1 += r.y * S[4 * q + 1];
+              S[4 * q + 2] = w.z * S[4 * q + 2] - au.z * uS + k.z * vj;
+              o0 += r.z * S[4 * q + 2];
+              S[4 * q + 3] = w.w * S[4 * q + 3] - au.w * uS + k.w * vj;
+              o1 += r.w * S[4 * q + 3];
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < NPT / 4; ++q) {
+              const float4 w = w4[q], u = u4[q], k = k4[q], r = r4[q];
+              o0 += r.x * (S[4 * q] + u.x * vj);
+              S[4 * q] = w.x * S[4 * q] + k.x * vj;
+              o1 += r.y * (S[4 * q + 1] + u.y * vj);
+              S[4 * q + 1] = w.y * S[4 * q + 1] + k.y * vj;
+              o0 += r.z * (S[4 * q + 2] + u.z * vj);
+              S[4 * q + 2] = w.z * S[4 * q + 2] + k.z * vj;
+              o1 += r.w * (S[4 * q + 3] + u.w * vj);
+              S[4 * q + 3] = w.w * S[4 * q + 3] + k.w * vj;
+            }
+          }
+          float o = o0 + o1;
+          for (int off = 1; off < KL; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+          if (on && slice == 0) o_c[t * N + col] = o;
+        }
       }
-      __syncthreads();
-    }
-    // -- decays, unit keys, rates: thread c serves channel c of every token of the chunk --------
-    if (on) {
-      const float w0 = a.w0[ch0 + tid];
-      const float extra = RULE == 1 ? a.rate_bias[ch0 + tid] : a.bonus[ch0 + tid];
-      for (int t = 0; t < nt; ++t) {
-        float z = 0.f;
-        for (int m = 0; m < R; ++m) z += th_s[t * R + m] * w2_s[m * N + tid];
-        z += w0;
-        const int i = t * N + tid;
-        if (RULE == 1) {
-          w_s[i] = expf(-a.decay_scale * sigmoidf(z));
-          const float u = k_s[i] * red_s[t];
+    } else {
+      // -- finish chunk c - 2: per head divide by the root mean square, weight, gate, scale ----------
+      const int fc = c - 2;
+      if (fc >= 0 && fc < n_chunks) {
+        const int nt = min(TC, T_len - fc * TC), t0 = fc * TC;
+        const float* o_c = o_s + (fc & 1) * TC * N;
+        float* red = red_s + TC;
+        for (int t = pwarp; t < nt; t += PROD / 32) {
+          float sq = 0.f;
+          for (int ch = plane; ch < N; ch += 32) sq += o_c[t * N + ch] * o_c[t * N + ch];
+          sq = warp_sum(sq);
+          if (plane == 0) red[t] = rsqrtf(sq / (float)N + a.eps);
+        }
+        producers_sync();
+        if (a.vec) {  // four channels at a time, four such pieces requested before the first is used
+          const int N4 = N / 4, items = nt * N4;
+          for (int i0 = pt; i0 < items; i0 += 4 * PROD) {
+            float g[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int i = i0 + u * PROD;
+              if (i < items) load4_el<T>(gp + (size_t)(row0 + t0 + i / N4) * a.g_stride + ch0 + 4 * (i % N4), g[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int i = i0 + u * PROD;
+              if (i >= items) continue;
+              const int t = i / N4, ch = 4 * (i % N4);
+              float o[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float gate = RULE == 1 ? sigmoidf(g[u][e]) : g[u][e] * sigmoidf(g[u][e]);
+                o[e] = o_c[t * N + ch + e] * red[t] * a.norm_w[ch0 + ch + e] * gate * a.out_scale;
+              }
+              store4_el<T>(outp + (size_t)(row0 + t0 + t) * a.out_stride + a.out_col + ch0 + ch, o);
+            }
+          }
+        } else
+        for (int i = pt; i < nt * N; i += PROD) {
+          const int t = i / N, ch = i % N;
           const size_t row = (size_t)(row0 + t0 + t);
-          u_s[i] = u;
-          au_s[i] = sigmoidf(to_float<T>(ap[row * a.rate_stride + ch0 + tid]) + extra) * u;
-        } else {
-          w_s[i] = expf(-expf(z));
-          u_s[i] = extra * k_s[i];
+          const float g = to_float<T>(gp[row * a.g_stride + ch0 + ch]);
+          const float gate = RULE == 1 ? sigmoidf(g) : g * sigmoidf(g);
+          outp[row * a.out_stride + a.out_col + ch0 + ch] =
+              from_float<T>(o_c[i] * red[t] * a.norm_w[ch0 + ch] * gate * a.out_scale);
+        }
+      }
+      // -- prepare chunk c ---------------------------------------------------------------------------
+      if (c < n_chunks) {
+        const int nt = min(TC, T_len - c * TC), t0 = c * TC;
+        float* buf = sm + (c & 1) * BUF;
+        float* r_s = buf;
+        float* k_s = buf + TC * VS;
+        float* w_s = buf + 2 * TC * VS;
+        float* u_s = buf + 3 * TC * VS;
+        float* au_s = buf + 4 * TC * VS;
+        float* v_s = buf + 5 * TC * VS;
+        producers_sync();  // th_s and red_s of the chunk before are no longer read
+        if (a.vec) {  // four channels at a time; two such pieces of every input requested before the first is used
+          const int N4 = N / 4, items = nt * N4;
+          for (int i0 = pt; i0 < items; i0 += 2 * PROD) {
+            float rv[2][4], kv[2][4], vv[2][4], av[2][4];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int i = i0 + u * PROD;
+              if (i >= items) continue;
+              const size_t row = (size_t)(row0 + t0 + i / N4);
+              const int ch = ch0 + 4 * (i % N4);
+              load4_el<T>(rp + row * a.r_stride + ch, rv[u]);
+              load4_el<T>(kp + row * a.k_stride + ch, kv[u]);
+              load4_el<T>(vp + row * a.v_stride + ch, vv[u]);
+              if (RULE == 1) load4_el<T>(ap + row * a.rate_stride + ch, av[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int i = i0 + u * PROD;
+              if (i >= items) continue;
+              const int t = i / N4, ch = 4 * (i % N4);
+              const int at = t * VS + (ch / NPT) * SL + (ch % NPT);
+              *reinterpret_cast<float4*>(r_s + at) = make_float4(rv[u][0], rv[u][1], rv[u][2], rv[u][3]);
+              *reinterpret_cast<float4*>(k_s + at) = make_float4(kv[u][0], kv[u][1], kv[u][2], kv[u][3]);
+              *reinterpret_cast<float4*>(v_s + t * N + ch) = make_float4(vv[u][0], vv[u][1], vv[u][2], vv[u][3]);
+              if (RULE == 1) *reinterpret_cast<float4*>(au_s + at) = make_float4(av[u][0], av[u][1], av[u][2], av[u][3]);
+            }
+          }
+        } else
+        for (int i = pt; i < nt * N; i += PROD) {
+          const int t = i / N, ch = i % N;
+          const size_t row = (size_t)(row0 + t0 + t);
+          const int at = t * VS + (ch / NPT) * SL + (ch % NPT);
+          r_s[at] = to_float<T>(rp[row * a.r_stride + ch0 + ch]);
+          k_s[at] = to_float<T>(kp[row * a.k_stride + ch0 + ch]);
+          v_s[i] = to_float<T>(vp[row * a.v_stride + ch0 + ch]);
+          if (RULE == 1) au_s[at] = to_float<T>(ap[row * a.rate_stride + ch0 + ch]);  // the raw rate, for now
+        }
+        for (int i = pt; i < nt * R; i += PROD) {
+          const int t = i / R, m = i % R;
+          th_s[i] = round_to<T>(tanhf(to_float<T>(lp[(size_t)(row0 + t0 + t) * a.lora_stride + m])));
+        }
+        producers_sync();
+        if (RULE == 1) {  // per token: sum of squared key channels
+          for (int t = pwarp; t < nt; t += PROD / 32) {
+            float sq = 0.f;
+            for (int ch = plane; ch < N; ch += 32) {
+              const float kv = k_s[t * VS + (ch / NPT) * SL + (ch % NPT)];
+              sq += kv * kv;
+            }
+            sq = warp_sum(sq);
+            if (plane == 0) red_s[t] = rsqrtf(sq + 1e-6f);
+          }
+          producers_sync();
+        }
+        for (int i = pt; i < nt * N; i += PROD) {
+          const int t = i / N, ch = i % N;
+          const int at = t * VS + (ch / NPT) * SL + (ch % NPT);
+          float z = 0.f;
+          for (int m = 0; m < R; ++m) z += th_s[t * R + m] * w2_s[m * N + ch];
+          z += a.w0[ch0 + ch];
+          if (RULE == 1) {
+            w_s[at] = expf(-a.decay_scale * sigmoidf(z));
+            const float u = k_s[at] * red_s[t];
+            u_s[at] = u;
+            au_s[at] = sigmoidf(au_s[at] + a.rate_bias[ch0 + ch]) * u;
+          } else {
+            w_s[at] = expf(-expf(z));
+            u_s[at] = a.bonus[ch0 + ch] * k_s[at];
+          }
         }
       }
     }
     __syncthreads();
-    // -- the scan: every thread alone with its column ----------------------------------------------
-    if (on) {
-      for (int t = 0; t < nt; ++t) {
-        const float* rr = r_s + t * N;
-        const float* kk = k_s + t * N;
-        const float* ww = w_s + t * N;
-        const float* uu = u_s + t * N;
-        const float vj = v_s[t * N + tid];
-        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-        if (RULE == 1) {
-          const float* aa = au_s + t * N;
-          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll
-          for (int i = 0; i < NCAP; i += 4) {
-            if (i < N) s0 += uu[i] * S[i];
-            if (i + 1 < N) s1 += uu[i + 1] * S[i + 1];
-            if (i + 2 < N) s2 += uu[i + 2] * S[i + 2];
-            if (i + 3 < N) s3 += uu[i + 3] * S[i + 3];
-          }
-          const float uS = (s0 + s1) + (s2 + s3);
-#pragma unroll
-          for (int i = 0; i < NCAP; i += 4) {
-            if (i < N) { S[i] = ww[i] * S[i] - aa[i] * uS + kk[i] * vj; o0 += rr[i] * S[i]; }
-            if (i + 1 < N) { S[i + 1] = ww[i + 1] * S[i + 1] - aa[i + 1] * uS + kk[i + 1] * vj; o1 += rr[i + 1] * S[i + 1]; }
-            if (i + 2 < N) { S[i + 2] = ww[i + 2] * S[i + 2] - aa[i + 2] * uS + kk[i + 2] * vj; o2 += rr[i + 2] * S[i + 2]; }
-            if (i + 3 < N) { S[i + 3] = ww[i + 3] * S[i + 3] - aa[i + 3] * uS + kk[i + 3] * vj; o3 += rr[i + 3] * S[i + 3]; }
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < NCAP; i += 4) {
-            if (i < N) { o0 += rr[i] * (S[i] + uu[i] * vj); S[i] = ww[i] * S[i] + kk[i] * vj; }
-            if (i + 1 < N) { o1 += rr[i + 1] * (S[i + 1] + uu[i + 1] * vj); S[i + 1] = ww[i + 1] * S[i + 1] + kk[i + 1] * vj; }
-            if (i + 2 < N) { o2 += rr[i + 2] * (S[i + 2] + uu[i + 2] * vj); S[i + 2] = ww[i + 2] * S[i + 2] + kk[i + 2] * vj; }
-            if (i + 3 < N) { o3 += rr[i + 3] * (S[i + 3] + uu[i + 3] * vj); S[i + 3] = ww[i + 3] * S[i + 3] + kk[i + 3] * vj; }
-          }
-        }
-        o_s[t * N + tid] = (o0 + o1) + (o2 + o3);
-      }
-    }
-    __syncthreads();
-    // -- per head: divide by the root mean square, weight, gate, scale --------------------------------
-    for (int t = warp; t < nt; t += n_warps) {
-      float sq = 0.f;
-      for (int c = lane; c < N; c += 32) sq += o_s[t * N + c] * o_s[t * N + c];
-      sq = warp_sum(sq);
-      if (lane == 0) red_s[t] = rsqrtf(sq / (float)N + a.eps);
-    }
-    __syncthreads();
-    for (int i = tid; i < nt * N; i += blockDim.x) {
-      const int t = i / N, c = i % N;
-      const size_t row = (size_t)(row0 + t0 + t);
-      const float g = to_float<T>(gp[row * a.g_stride + ch0 + c]);
-      const float gate = RULE == 1 ? sigmoidf(g) : g * sigmoidf(g);
-      outp[row * a.out_stride + a.out_col + ch0 + c] =
-          from_float<T>(o_s[i] * red_s[t] * a.norm_w[ch0 + c] * gate * a.out_scale);
-    }
   }
 #pragma unroll
-  for (int i = 0; i < NCAP; ++i)
-    if (on && i < N) st[(size_t)i * N + tid] = S[i];
+  for (int i = 0; i < NPT; ++i)
+    if (on && key0 + i < N) st[(size_t)(key0 + i) * N + col] = S[i];
   if (a.last_rows && head == 0 && T_len > 0) {
     const T* last = reinterpret_cast<const T*>(a.last_rows) + (size_t)(row0 + T_len - 1) * a.last_stride;
     float* dst = a.last_state + (size_t)slot * a.C;
-    for (int c = tid; c < a.C; c += blockDim.x) dst[c] = to_float<T>(last[c]);
+    for (int ch = tid; ch < a.C; ch += blockDim.x) dst[ch] = to_float<T>(last[ch]);
   }
 }
 
-template <typename T, int RULE, int NCAP>
+template <typename T, int RULE, int NPT, int TC, int MAXT>
 int launch_recurrence(const ScanArgs& a, cudaStream_t stream) {
-  constexpr int TC = NCAP <= 64 ? 16 : 8;
-  const size_t smem = ((size_t)7 * TC * a.N + (size_t)a.R * a.N + (size_t)TC * a.R + TC) * sizeof(float);
-  if (smem > 200 * 1024) return -2;
-  auto kern = recurrence_kernel<T, RULE, NCAP, TC>;
+  int KL = 1;
+  while (KL * NPT < a.N) KL <<= 1;
+  const int cons = ((a.N * KL + 31) / 32) * 32;
+  if (cons + PROD > MAXT) return -2;
+  const size_t buf = (size_t)5 * TC * KL * (NPT + 4) + (size_t)TC * a.N;
+  const size_t smem = (2 * buf + (size_t)2 * TC * a.N + (size_t)a.R * a.N + (size_t)TC * a.R + 2 * TC) * sizeof(float);
+  if (smem > 220 * 1024) return -2;
+  auto kern = recurrence_kernel<T, RULE, NPT, TC, MAXT>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return (int)launch_pdl(kern, dim3(a.n_seqs * a.H), dim3(NCAP), smem, stream, a);
+  return (int)launch_pdl(kern, dim3(a.n_seqs * a.H), dim3(cons + PROD), smem, stream, a, KL, cons);
 }
 
 template <typename T, int RULE>
 int pick_recurrence(const ScanArgs& a, cudaStream_t stream) {
-  if (a.N <= 32) return launch_recurrence<T, RULE, 32>(a, stream);
-  if (a.N <= 64) return launch_recurrence<T, RULE, 64>(a, stream);
-  if (a.N <= 128) return launch_recurrence<T, RULE, 128>(a, stream);
-  return -2;  // a head's state column no longer fits one thread's registers
+  if (a.N <= 64) return launch_recurrence<T, RULE, 16, 32, 256 + PROD>(a, stream);
+  if (a.N <= 128) return launch_recurrence<T, RULE, 32, 16, 512 + PROD>(a, stream);
+  return -2;  // a head's state no longer fits the registers of one block
 }
 
 }  // namespace
@@ -270,6 +401,12 @@ KRK_API int krk_linear_recurrence(int rule, const void* r, int r_stride, const v
   a.out = out; a.out_stride = out_stride; a.out_col = out_col; a.out_scale = out_scale; a.eps = eps;
   a.decay_scale = decay_scale; a.H = H; a.N = N; a.R = R; a.n_seqs = n_seqs;
   a.cu_q = cu_q; a.seq_qlen = seq_qlen; a.seq_slot = seq_slot;
+  {
+    const uintptr_t mask = dtype == KRK_DTYPE_F32 ? 15 : 7;
+    const uintptr_t ptrs = (uintptr_t)r | (uintptr_t)k | (uintptr_t)v | (uintptr_t)g | (uintptr_t)rate | (uintptr_t)out;
+    const int strides = r_stride | k_stride | v_stride | g_stride | rate_stride | out_stride | out_col | N;
+    a.vec = (ptrs & mask) == 0 && (strides & 3) == 0;
+  }
   if (rule != 0 && rule != 1) return -2;
   if (rule == 1 && (!rate || !rate_bias)) return -2;
   if (rule == 0 && !bonus) return -2;

@@ -15,6 +15,12 @@
 // the weights, kept in float32, multiply the values with the lanes spread over the value
 // head. A row's result depends on that row's keys only, in their order, so it is the same to
 // the bit however the tokens were cut into steps or batched.
+//
+// krk_sink_attention_single (steps of one token per sequence): one block per (sequence, kv head).
+// Its warps take the window's 32-key chunks in turn, each lane scores its key against every query head
+// of the group from one read of the key (and every value row serves all of the group's heads), and the
+// warps' running (maximum, sum, output) are merged in warp order at the end; the sink enters once, as
+// the first warp's starting state.
 #include "common.cuh"
 
 namespace {
@@ -147,9 +153,10 @@ __global__ void sink_attention_kernel(T* __restrict__ out, int out_stride, int o
   for (int base = first; base <= pos; base += 32) {
     const int key = base + lane;
     float s = -INFINITY;
+    int my_page = 0;
     if (key <= pos) {
-      const int page = page_of(table, width, slot, key);
-      s = dot_row<T>(qs, k_cache + (((size_t)page * HKV + kh) * KRK_PAGE + (key % KRK_PAGE)) * D, D) * scale;
+      my_page = page_of(table, width, slot, key);
+      s = dot_row<T>(qs, k_cache + (((size_t)my_page * HKV + kh) * KRK_PAGE + (key % KRK_PAGE)) * D, D) * scale;
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float alpha = expf(m - m_new);  // exp(-inf) = 0 before the first key when there is no sink
@@ -158,10 +165,11 @@ __global__ void sink_attention_kernel(T* __restrict__ out, int out_stride, int o
 #pragma unroll
     for (int i = 0; i < MAX_V_PER_LANE; ++i) acc[i] *= alpha;
     const int n = min(32, pos - base + 1);
+#pragma unroll 4
     for (int j = 0; j < n; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const int kj = base + j;
-      const int page = page_of(table, width, slot, kj);
+      const int page = __shfl_sync(0xffffffffu, my_page, j);  // lane j looked its key's page up already
       const T* vp = v_cache + (((size_t)page * HKV + kh) * KRK_PAGE + (kj % KRK_PAGE)) * DV;
 #pragma unroll
       for (int i = 0; i < MAX_V_PER_LANE; ++i) {
@@ -177,6 +185,202 @@ __global__ void sink_attention_kernel(T* __restrict__ out, int out_stride, int o
   for (int i = 0; i < MAX_V_PER_LANE; ++i) {
     const int d = lane + 32 * i;
     if (d < DV) o[d] = from_float<T>(acc[i] * inv);
+  }
+}
+
+constexpr int GROUP_MAX = 8;       // query heads of one kv head that a block serves at once
+constexpr int SINGLE_WARPS = 16;
+
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* f);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* f) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) f[j] = p[j];
+}
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float* f) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    f[2 * j] = __low2float(h[j]);
+    f[2 * j + 1] = __high2float(h[j]);
+  }
+}
+
+template <typename T> __device__ __forceinline__ void load4(const T* p, float* f, bool on);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float* f, bool on) {
+  const float4 v = on ? *reinterpret_cast<const float4*>(p) : make_float4(0.f, 0.f, 0.f, 0.f);
+  f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4<bf16>(const bf16* p, float* f, bool on) {
+  const uint2 raw = on ? *reinterpret_cast<const uint2*>(p) : make_uint2(0u, 0u);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  f[0] = __low2float(h[0]); f[1] = __high2float(h[0]); f[2] = __low2float(h[1]); f[3] = __high2float(h[1]);
+}
+
+// V4: value heads of a multiple of 4 elements up to 128, lane l holding elements 4l .. 4l + 3 of a row
+template <typename T, bool V4>
+__global__ void __launch_bounds__(SINGLE_WARPS * 32)
+sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, float out_scale,
+                             const T* __restrict__ proj, int stride, int q_col, int HQ, int HKV, int D, int DV,
+                             const float* __restrict__ sink, const int* __restrict__ seq_slot,
+                             const int* __restrict__ seq_start, const int* __restrict__ table, int width,
+                             const T* __restrict__ k_cache, const T* __restrict__ v_cache, float scale, int window,
+                             int g0, int GN) {
+  extern __shared__ __align__(16) float sm1[];
+  float* q_s = sm1;                       // [GN][D]
+  float* part = q_s + GN * D;             // [warps][GN][DV + 2]
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int seq = blockIdx.x / HKV, kh = blockIdx.x % HKV;
+  const int G = HQ / HKV;
+  const int head0 = kh * G + g0;          // the block's first query head
+  const int pos = seq_start[seq];         // the one new token sits at the sequence's length before the step
+  const int slot = seq_slot[seq];
+  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  const T* q = proj + (size_t)seq * stride + q_col + (size_t)head0 * D;
+  for (int i = threadIdx.x; i < GN * D; i += blockDim.x) q_s[i] = to_float<T>(q[i]);
+  __syncthreads();
+
+  float m[GROUP_MAX], l[GROUP_MAX], acc[GROUP_MAX][MAX_V_PER_LANE / 2];
+#pragma unroll
+  for (int g = 0; g < GROUP_MAX; ++g) {
+    const bool has = warp == 0 && sink != nullptr && g < GN;
+    m[g] = has ? sink[head0 + g] : -INFINITY;
+    l[g] = has ? 1.f : 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) acc[g][i] = 0.f;
+  }
+  const bool vec = (D & 7) == 0;  // rows of the cache then start on 16-byte boundaries (32 for float)
+  for (int base = first + 32 * warp; base <= pos; base += 32 * SINGLE_WARPS) {
+    const int key = base + lane;
+    float s[GROUP_MAX];
+#pragma unroll
+    for (int g = 0; g < GROUP_MAX; ++g) s[g] = 0.f;
+    int my_page = 0;
+    if (key <= pos) {
+      my_page = page_of(table, width, slot, key);
+      const T* kp = k_cache + (((size_t)my_page * HKV + kh) * KRK_PAGE + (key % KRK_PAGE)) * D;
+      if (vec) {
+        // 32 elements of the key row are requested at once (a row is a lane's own, nothing shares its
+        // latency), then multiplied with every head's query
+        int d = 0;
+        for (; d + 32 <= D; d += 32) {
+          float kf[4][8];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) load8<T>(kp + d + 8 * c, kf[c]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int g = 0; g < GROUP_MAX; ++g)
+              if (g < GN) {
+                const float4 qa = *reinterpret_cast<const float4*>(q_s + g * D + d + 8 * c);
+                const float4 qb = *reinterpret_cast<const float4*>(q_s + g * D + d + 8 * c + 4);
+                s[g] += qa.x * kf[c][0] + qa.y * kf[c][1] + qa.z * kf[c][2] + qa.w * kf[c][3] + qb.x * kf[c][4] +
+                        qb.y * kf[c][5] + qb.z * kf[c][6] + qb.w * kf[c][7];
+              }
+        }
+        for (; d < D; d += 8) {
+          float kf[8];
+          load8<T>(kp + d, kf);
+#pragma unroll
+          for (int g = 0; g < GROUP_MAX; ++g)
+            if (g < GN) {
+              const float4 qa = *reinterpret_cast<const float4*>(q_s + g * D + d);
+              const float4 qb = *reinterpret_cast<const float4*>(q_s + g * D + d + 4);
+              s[g] += qa.x * kf[0] + qa.y * kf[1] + qa.z * kf[2] + qa.w * kf[3] + qb.x * kf[4] + qb.y * kf[5] +
+                      qb.z * kf[6] + qb.w * kf[7];
+            }
+        }
+      } else {
+        for (int d = 0; d < D; ++d) {
+          const float kf = to_float<T>(kp[d]);
+#pragma unroll
+          for (int g = 0; g < GROUP_MAX; ++g)
+            if (g < GN) s[g] += q_s[g * D + d] * kf;
+        }
+      }
+    }
+    float p[GROUP_MAX];
+#pragma unroll
+    for (int g = 0; g < GROUP_MAX; ++g) {
+      if (g >= GN) continue;
+      const float sc = key <= pos ? s[g] * scale : -INFINITY;
+      const float m_new = fmaxf(m[g], warp_max(sc));
+      const float alpha = expf(m[g] - m_new);
+      p[g] = key <= pos ? expf(sc - m_new) : 0.f;
+      l[g] = l[g] * alpha + warp_sum(p[g]);
+#pragma unroll
+      for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) acc[g][i] *= alpha;
+      m[g] = m_new;
+    }
+    const int n = min(32, pos - base + 1);
+    for (int j0 = 0; j0 < n; j0 += 8) {  // eight value rows are requested before the first is used
+      float vf[8][MAX_V_PER_LANE / 2];
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        const int j = j0 + jj;
+        const int kj = base + j;
+        const int page = __shfl_sync(0xffffffffu, my_page, j & 31);  // lane j looked its key's page up already
+        const T* vp = v_cache + (((size_t)page * HKV + kh) * KRK_PAGE + (kj % KRK_PAGE)) * DV;
+        if (V4) {  // four neighbouring elements per lane, one load
+          load4<T>(vp + 4 * lane, vf[jj], j < n && 4 * lane < DV);
+        } else {
+#pragma unroll
+          for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) {
+            const int d = lane + 32 * i;
+            vf[jj][i] = (j < n && d < DV) ? to_float<T>(vp[d]) : 0.f;
+          }
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj)
+#pragma unroll
+        for (int g = 0; g < GROUP_MAX; ++g) {
+          if (g >= GN) continue;
+          const float pj = __shfl_sync(0xffffffffu, p[g], (j0 + jj) & 31);  // zero beyond the last key
+#pragma unroll
+          for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) acc[g][i] += pj * vf[jj][i];
+        }
+    }
+  }
+  // the warps' partial results, then one warp per head merges them in warp order
+  const int PS = DV + 2;
+#pragma unroll
+  for (int g = 0; g < GROUP_MAX; ++g) {
+    if (g >= GN) continue;
+    float* dst = part + ((size_t)warp * GN + g) * PS;
+    if (lane == 0) { dst[DV] = m[g]; dst[DV + 1] = l[g]; }
+#pragma unroll
+    for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) {
+      const int d = V4 ? 4 * lane + i : lane + 32 * i;
+      if (d < DV) dst[d] = acc[g][i];
+    }
+  }
+  __syncthreads();
+  for (int g = warp; g < GN; g += SINGLE_WARPS) {
+    float mx = -INFINITY;
+    for (int w = 0; w < SINGLE_WARPS; ++w) mx = fmaxf(mx, part[((size_t)w * GN + g) * PS + DV]);
+    float total = 0.f, o[MAX_V_PER_LANE / 2];
+#pragma unroll
+    for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) o[i] = 0.f;
+    for (int w = 0; w < SINGLE_WARPS; ++w) {
+      const float* src = part + ((size_t)w * GN + g) * PS;
+      const float f = src[DV] == -INFINITY ? 0.f : expf(src[DV] - mx);
+      total += src[DV + 1] * f;
+#pragma unroll
+      for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) {
+        const int d = V4 ? 4 * lane + i : lane + 32 * i;
+        if (d < DV) o[i] += src[d] * f;
+      }
+    }
+    T* op = out + (size_t)seq * out_stride + out_col + (size_t)(head0 + g) * DV;
+    const float inv = out_scale / total;
+#pragma unroll
+    for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) {
+      const int d = V4 ? 4 * lane + i : lane + 32 * i;
+      if (d < DV) op[d] = from_float<T>(o[i] * inv);
+    }
   }
 }
 
@@ -220,4 +424,41 @@ KRK_API int krk_sink_attention(void* out, int out_stride, int out_col, float out
   return (int)launch_pdl(sink_attention_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, (bf16*)out,
                          out_stride, out_col, out_scale, (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink, row_seq,
                          row_pos, seq_slot, table, width, (const bf16*)k_cache, (const bf16*)v_cache, rows, scale, window);
+}
+
+// One token per sequence: rows are the sequences, in order. Value heads of up to 128 elements; others take
+// krk_sink_attention.
+KRK_API int krk_sink_attention_single(void* out, int out_stride, int out_col, float out_scale, const void* proj, int stride,
+                                      int q_col, int HQ, int HKV, int D, int DV, const float* sink, const int* seq_slot,
+                                      const int* seq_start, const int* table, int width, const void* k_cache,
+                                      const void* v_cache, int n_seqs, float scale, int window, int dtype,
+                                      cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  if (DV > 32 * (MAX_V_PER_LANE / 2) || D > 1024) return -2;
+  const int G = HQ / HKV;
+  for (int g0 = 0; g0 < G; g0 += GROUP_MAX) {
+    const int GN = min(GROUP_MAX, G - g0);
+    const size_t smem = ((size_t)GN * D + (size_t)SINGLE_WARPS * GN * (DV + 2)) * sizeof(float);
+    if (smem > 96 * 1024) return -2;
+    cudaError_t e;
+    const bool v4 = (DV & 3) == 0;  // rows of the value cache then start on 8-byte (16 for float) boundaries
+    if (smem > 48 * 1024) {
+      cudaFuncSetAttribute(sink_attention_single_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      cudaFuncSetAttribute(sink_attention_single_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      cudaFuncSetAttribute(sink_attention_single_kernel<bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      cudaFuncSetAttribute(sink_attention_single_kernel<bf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    }
+    if (dtype == KRK_DTYPE_F32)
+      e = launch_pdl(v4 ? sink_attention_single_kernel<float, true> : sink_attention_single_kernel<float, false>,
+                     dim3(n_seqs * HKV), dim3(SINGLE_WARPS * 32), smem, stream,
+                     (float*)out, out_stride, out_col, out_scale, (const float*)proj, stride, q_col, HQ, HKV, D, DV, sink,
+                     seq_slot, seq_start, table, width, (const float*)k_cache, (const float*)v_cache, scale, window, g0, GN);
+    else
+      e = launch_pdl(v4 ? sink_attention_single_kernel<bf16, true> : sink_attention_single_kernel<bf16, false>,
+                     dim3(n_seqs * HKV), dim3(SINGLE_WARPS * 32), smem, stream,
+                     (bf16*)out, out_stride, out_col, out_scale, (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink,
+                     seq_slot, seq_start, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale, window, g0, GN);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
 }

@@ -23,27 +23,75 @@ __global__ void embed_scaled_kernel(float* __restrict__ out, const T* __restrict
   for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = bad ? 0.f : to_float<T>(src[i]) * scale;
 }
 
-template <typename T>
+template <typename T> __device__ __forceinline__ void load4_rows(const T* p, float* f);
+template <> __device__ __forceinline__ void load4_rows<float>(const float* p, float* f) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4_rows<bf16>(const bf16* p, float* f) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  f[0] = __low2float(h[0]); f[1] = __high2float(h[0]); f[2] = __low2float(h[1]); f[3] = __high2float(h[1]);
+}
+template <typename T> __device__ __forceinline__ void store4_rows(T* p, const float* f);
+template <> __device__ __forceinline__ void store4_rows<float>(float* p, const float* f) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+template <> __device__ __forceinline__ void store4_rows<bf16>(bf16* p, const float* f) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned*>(&a);
+  raw.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename T, bool VEC>
 __global__ void rmsnorm_wide_kernel(T* __restrict__ out, float* x_new, const float* x, const T* __restrict__ branch,
                                     const float* __restrict__ gain, float offset, int H, float eps) {
-  extern __shared__ float row_s[];  // H floats
+  extern __shared__ __align__(16) float row_s[];  // H floats
   __shared__ float scratch[32];
   grid_launch_dependents();
   grid_dependency_wait();
   const size_t base = (size_t)blockIdx.x * H;
   float sq = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float f = x[base + i];
-    if (branch) {
-      f += to_float<T>(branch[base + i]);
-      x_new[base + i] = f;
+  if (VEC) {  // H a multiple of 4: 16-byte pieces of the stream, 8- or 16-byte pieces of the branch and the result
+    const float4* xv = reinterpret_cast<const float4*>(x + base);
+    float4* nv = reinterpret_cast<float4*>(x_new + base);
+    for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
+      float4 f = xv[i];
+      if (branch) {
+        float b[4];
+        load4_rows<T>(branch + base + 4 * i, b);
+        f.x += b[0]; f.y += b[1]; f.z += b[2]; f.w += b[3];
+        nv[i] = f;
+      }
+      reinterpret_cast<float4*>(row_s)[i] = f;
+      sq += f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
     }
-    row_s[i] = f;
-    sq += f * f;
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float f = x[base + i];
+      if (branch) {
+        f += to_float<T>(branch[base + i]);
+        x_new[base + i] = f;
+      }
+      row_s[i] = f;
+      sq += f * f;
+    }
   }
   const float rstd = rsqrtf(block_sum(sq, scratch) / (float)H + eps);
-  for (int i = threadIdx.x; i < H; i += blockDim.x)
-    out[base + i] = from_float<T>(row_s[i] * rstd * (offset + gain[i]));
+  if (VEC) {
+    for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
+      const float4 f = reinterpret_cast<const float4*>(row_s)[i];
+      const float4 g = reinterpret_cast<const float4*>(gain)[i];
+      const float r[4] = {f.x * rstd * (offset + g.x), f.y * rstd * (offset + g.y), f.z * rstd * (offset + g.z),
+                          f.w * rstd * (offset + g.w)};
+      store4_rows<T>(out + base + 4 * i, r);
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+      out[base + i] = from_float<T>(row_s[i] * rstd * (offset + gain[i]));
+  }
 }
 
 __device__ __forceinline__ float activation(float z, int act) {
@@ -53,11 +101,22 @@ __device__ __forceinline__ float activation(float z, int act) {
 }
 
 // out[r, i] = round(act(g) * u), g = gu[r, i], u = gu[r, I + i]
-template <typename T>
+template <typename T, bool VEC>
 __global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, int gu_stride, int I, int act) {
   grid_launch_dependents();
   grid_dependency_wait();
   const size_t r = blockIdx.x;
+  if (VEC) {  // I and the row stride multiples of 4
+    for (int i = 4 * (blockIdx.y * blockDim.x + threadIdx.x); i < I; i += 4 * gridDim.y * blockDim.x) {
+      float g[4], u[4], o[4];
+      load4_rows<T>(gu + r * gu_stride + i, g);
+      load4_rows<T>(gu + r * gu_stride + I + i, u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = activation(g[j], act) * u[j];
+      store4_rows<T>(out + r * I + i, o);
+    }
+    return;
+  }
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
     const float g = to_float<T>(gu[r * gu_stride + i]);
     const float u = to_float<T>(gu[r * gu_stride + I + i]);
@@ -83,7 +142,8 @@ static int launch_rmsnorm_wide(void* out, float* x_new, const float* x, const vo
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 220 * 1024) return -2;
   const int threads = H >= 4096 ? 1024 : (H >= 1024 ? 256 : 128);
-  auto kern = rmsnorm_wide_kernel<T>;
+  const bool vec = H % 4 == 0 && ((uintptr_t)gain & 15) == 0;
+  auto kern = vec ? rmsnorm_wide_kernel<T, true> : rmsnorm_wide_kernel<T, false>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   return (int)launch_pdl(kern, dim3(rows), dim3(threads), smem, stream, (T*)out, x_new, x, (const T*)branch, gain, offset,
                          H, eps);
@@ -99,10 +159,12 @@ KRK_API int krk_rmsnorm_wide(void* out, float* x_new, const float* x, const void
 KRK_API int krk_gated_act(void* out, const void* gu, int gu_stride, int rows, int I, int act, int dtype,
                           cudaStream_t stream) {
   if (rows == 0) return 0;
-  const int chunks = min(64, (I + 255) / 256);
+  const size_t esz = dtype == KRK_DTYPE_F32 ? 4 : 2;
+  const bool vec = I % 4 == 0 && gu_stride % 4 == 0 && ((uintptr_t)gu & (4 * esz - 1)) == 0;
+  const int chunks = min(64, (I / (vec ? 4 : 1) + 255) / 256);
   if (dtype == KRK_DTYPE_F32)
-    return (int)launch_pdl(gated_act_kernel<float>, dim3(rows, chunks), dim3(256), 0, stream, (float*)out,
-                           (const float*)gu, gu_stride, I, act);
-  return (int)launch_pdl(gated_act_kernel<bf16>, dim3(rows, chunks), dim3(256), 0, stream, (bf16*)out, (const bf16*)gu,
-                         gu_stride, I, act);
+    return (int)launch_pdl(vec ? gated_act_kernel<float, true> : gated_act_kernel<float, false>, dim3(rows, chunks),
+                           dim3(256), 0, stream, (float*)out, (const float*)gu, gu_stride, I, act);
+  return (int)launch_pdl(vec ? gated_act_kernel<bf16, true> : gated_act_kernel<bf16, false>, dim3(rows, chunks), dim3(256),
+                         0, stream, (bf16*)out, (const bf16*)gu, gu_stride, I, act);
 }

@@ -55,6 +55,11 @@ class SinkWindowAttention(Branch):
     def cache_need(self):
         return KVNeed(self.kv_heads, self.dim, self.window, None if self.vdim == self.dim else self.vdim)
 
+    def attention_head_dims(self):
+        """Steps of many tokens in bfloat16 run on the tensor cores where key and value heads have one size that
+        is a multiple of 16: that kernel is compiled per head size."""
+        return (self.dim,) if self.dim == self.vdim and self.dim % 16 == 0 and self.dim <= 256 else ()
+
     def bind(self, tensors, runtime):
         self.w = {k: tensors[k] for k in ("q", "k", "v", "o")}
         self.sink = tensors["sink"].float().contiguous() if self.has_sink else None

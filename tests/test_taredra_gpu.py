@@ -27,7 +27,9 @@ def runtime(dtype):
     from kernel_rush_kawk_b200.csrc import load_kernels
     from kernel_rush_kawk_b200.engine.model import Runtime
 
-    return Runtime(torch.device("cuda:0"), dtype, load_kernels(()))
+    # with the per-head-size attention libraries of the sizes below loaded, bfloat16 steps of many tokens whose key
+    # and value heads have one of these sizes take the tensor-core kernel; all others the general one
+    return Runtime(torch.device("cuda:0"), dtype, load_kernels((16, 32, 64)))
 
 
 def rand(shape, seed, scale=1.0):
@@ -392,7 +394,10 @@ def test_unequal_requests_in_one_batch_equal_each_alone(folders, dtype):
     for i, seq in enumerate(seqs):
         both = torch.cat(got[i])
         assert_logits(both, plain_logits(folders[name], seq), dtype, f"request {i} in the batch")
-        if dtype == "float32":  # every sum of the 32-bit path is ordered per row: nothing depends on the batch
+        if dtype == "float32" and len(seq) > 1:
+            # every sum of the 32-bit path is ordered per row, so nothing depends on the batch. (A prompt of one
+            # token is a single-token step alone and a row of a many-token step in the batch: two kernels for the
+            # attention, equal up to rounding.)
             assert torch.equal(both, alone[i]), f"request {i}: batched and alone differ"
         else:
             assert spread(both, alone[i]).max() < 2e-2
