@@ -247,7 +247,7 @@ class Kernels:
                  "tcgen05 gemm")
         return out
 
-    def _skinny(self, x, w, out_dtype, swiglu_rows=0):
+    def _skinny(self, x, w, out_dtype, swiglu_rows=0, gate_act=1):
         """x: a tensor or a Normed not yet computed (then the add and the norm run in
         the kernel's prologue)."""
         lazy = not isinstance(x, torch.Tensor)
@@ -261,7 +261,7 @@ class Kernels:
         self._ok(self.core.krk_skinny_linear(
             out.data_ptr(), src.data_ptr(), w.data_ptr(), _ptr(branch), _ptr(gain), _ptr(x_new),
             int(gain is not None and gain.dtype == torch.float32), None, M, N, K, float(x.eps) if lazy else 0.0,
-            int(swiglu_rows > 0), _code(out_dtype), self._stream()), "skinny product")
+            int(gate_act if swiglu_rows > 0 else 0), _code(out_dtype), self._stream()), "skinny product")
         if lazy:
             x.mark_fused()
         return out
@@ -492,6 +492,8 @@ class Kernels:
         """act(gate h) * (up h) with W = cat(gate, up); silu on few bfloat16 rows runs in the product's epilogue."""
         if activation == "silu" and self._use_skinny(h, w_gate_up):
             return self.gate_up_swiglu(h, w_gate_up, intermediate)
+        if activation == "gelu_tanh" and self._use_skinny(h, w_gate_up):  # few rows: in the product's epilogue
+            return self._skinny(self._resolve(h), w_gate_up, w_gate_up.dtype, swiglu_rows=intermediate, gate_act=2)
         return self.gated_act(self.linear(h, w_gate_up), intermediate, activation)
 
     def rotate_norm_write(self, proj, q_col, k_col, v_col, heads, kv_heads, dim, vdim, inv_freq, rot_dims, value_eps,

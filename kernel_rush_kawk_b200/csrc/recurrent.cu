@@ -88,20 +88,22 @@ template <> __device__ __forceinline__ void store4_el<bf16>(bf16* p, const float
 
 __device__ __forceinline__ float sigmoidf(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-constexpr int PROD = 128;  // threads that prepare and finish chunks beside the threads that scan
+constexpr int CPT = 2;     // columns of S per scanning thread: every staged vector it reads serves both
 
-__device__ __forceinline__ void producers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(PROD) : "memory"); }
+template <int PROD>
+__device__ __forceinline__ void producers_sync_n() { asm volatile("bar.sync 1, %0;" ::"n"(PROD) : "memory"); }
 
 // NPT: key channels of a column that one lane keeps (16 for heads of up to 64 channels, 32 up to 128).
 // A lane's slice of a staged vector starts NPT + 4 floats after its neighbour's, so that the four
 // slices a quarter-warp reads at once fall into different banks. TC: tokens per chunk.
 //
-// The block's first `cons` threads scan; its last PROD threads prepare the chunk after the one being
+// The block's first `cons` threads scan; its last PROD threads (a multiple of 32) prepare the chunk after the one being
 // scanned (stage r, k, v; unit-key norms; decays and rates) into the other of two buffers and finish the
 // chunk before it (per-head norm, weight, gate, store). The two groups meet once per chunk.
-template <typename T, int RULE, int NPT, int TC, int MAXT>
+template <typename T, int RULE, int NPT, int TC, int PROD, int MAXT>
 __global__ void __launch_bounds__(MAXT, 1) recurrence_kernel(ScanArgs a, int KL, int cons) {
   constexpr int SL = NPT + 4;
+  auto producers_sync = [] { producers_sync_n<PROD>(); };
   extern __shared__ __align__(16) float sm[];
   const int N = a.N, R = a.R;
   const int VS = KL * SL;            // floats of one staged vector of one token
@@ -127,13 +129,17 @@ __global__ void __launch_bounds__(MAXT, 1) recurrence_kernel(ScanArgs a, int KL,
   const bool consumer = tid < cons;
   float* st = a.state + (((size_t)slot * a.H + head) * N) * N;
 
-  // consumer: value channel `col`, key channels key0 .. key0 + NPT - 1
-  const int col = tid / KL, slice = tid % KL;
-  const bool on = consumer && col < N;
+  // consumer: value channels col0 .. col0 + CPT - 1, key channels key0 .. key0 + NPT - 1
+  const int col0 = (tid / KL) * CPT, slice = tid % KL;
   const int key0 = slice * NPT;
-  float S[NPT];
+  bool on[CPT];
+  float S[CPT][NPT];
 #pragma unroll
-  for (int i = 0; i < NPT; ++i) S[i] = (on && key0 + i < N) ? st[(size_t)(key0 + i) * N + col] : 0.f;
+  for (int c2 = 0; c2 < CPT; ++c2) {
+    on[c2] = consumer && col0 + c2 < N;
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) S[c2][i] = (on[c2] && key0 + i < N) ? st[(size_t)(key0 + i) * N + col0 + c2] : 0.f;
+  }
 
   // producer
   const int pt = tid - cons, plane = pt & 31, pwarp = pt >> 5;
@@ -160,50 +166,73 @@ __global__ void __launch_bounds__(MAXT, 1) recurrence_kernel(ScanArgs a, int KL,
           const float4* k4 = reinterpret_cast<const float4*>(buf + TC * VS + at);
           const float4* w4 = reinterpret_cast<const float4*>(buf + 2 * TC * VS + at);
           const float4* u4 = reinterpret_cast<const float4*>(buf + 3 * TC * VS + at);
-          const float vj = on ? v_s[t * N + col] : 0.f;
-          float o0 = 0.f, o1 = 0.f;
+          float vj[CPT], o0[CPT], o1[CPT];
+#pragma unroll
+          for (int c2 = 0; c2 < CPT; ++c2) {
+            vj[c2] = on[c2] ? v_s[t * N + col0 + c2] : 0.f;
+            o0[c2] = o1[c2] = 0.f;
+          }
           if (RULE == 1) {
             const float4* a4 = reinterpret_cast<const float4*>(buf + 4 * TC * VS + at);
-            float s0 = 0.f, s1 = 0.f;
+            float s0[CPT], s1[CPT], uS[CPT];
+#pragma unroll
+            for (int c2 = 0; c2 < CPT; ++c2) s0[c2] = s1[c2] = 0.f;
 #pragma unroll
             for (int q = 0; q < NPT / 4; ++q) {
               const float4 u = u4[q];
-              s0 += u.x * S[4 * q];
-              s1 += u.y * S[4 * q + 1];
-              s0 += u.z * S[4 * q + 2];
-              s1 += u.w * S[4 * q + 3];
+#pragma unroll
+              for (int c2 = 0; c2 < CPT; ++c2) {
+                s0[c2] += u.x * S[c2][4 * q];
+                s1[c2] += u.y * S[c2][4 * q + 1];
+                s0[c2] += u.z * S[c2][4 * q + 2];
+                s1[c2] += u.w * S[c2][4 * q + 3];
+              }
             }
-            float uS = s0 + s1;
-            for (int off = 1; off < KL; off <<= 1) uS += __shfl_xor_sync(0xffffffffu, uS, off);
+#pragma unroll
+            for (int c2 = 0; c2 < CPT; ++c2) {
+              uS[c2] = s0[c2] + s1[c2];
+              for (int off = 1; off < KL; off <<= 1) uS[c2] += __shfl_xor_sync(0xffffffffu, uS[c2], off);
+            }
 #pragma unroll
             for (int q = 0; q < NPT / 4; ++q) {
               const float4 w = w4[q], au = a4[q], k = k4[q], r = r4[q];
-              S[4 * q] = w.x * S[4 * q] - au.x * uS + k.x * vj;
-              o0 += r.x * S[4 * q];
-              S[4 * q + 1] = w.y * S[4 * q + 1] - au.y * uS + k.y * vj;
-              o1 += r.y * S[4 * q + 1];
-              S[4 * q + 2] = w.z * S[4 * q + 2] - au.z * uS + k.z * vj;
-              o0 += r.z * S[4 * q + 2];
-              S[4 * q + 3] = w.w * S[4 * q + 3] - au.w * uS + k.w * vj;
-              o1 += r.w * S[4 * q + 3];
+#pragma unroll
+              for (int c2 = 0; c2 < CPT; ++c2) {
+                float* Sc = S[c2];
+                Sc[4 * q] = w.x * Sc[4 * q] - au.x * uS[c2] + k.x * vj[c2];
+                o0[c2] += r.x * Sc[4 * q];
+                Sc[4 * q + 1] = w.y * Sc[4 * q + 1] - au.y * uS[c2] + k.y * vj[c2];
+                o1[c2] += r.y * Sc[4 * q + 1];
+                Sc[4 * q + 2] = w.z * Sc[4 * q + 2] - au.z * uS[c2] + k.z * vj[c2];
+                o0[c2] += r.z * Sc[4 * q + 2];
+                Sc[4 * q + 3] = w.w * Sc[4 * q + 3] - au.w * uS[c2] + k.w * vj[c2];
+                o1[c2] += r.w * Sc[4 * q + 3];
+              }
             }
           } else {
 #pragma unroll
             for (int q = 0; q < NPT / 4; ++q) {
               const float4 w = w4[q], u = u4[q], k = k4[q], r = r4[q];
-              o0 += r.x * (S[4 * q] + u.x * vj);
-              S[4 * q] = w.x * S[4 * q] + k.x * vj;
-              o1 += r.y * (S[4 * q + 1] + u.y * vj);
-              S[4 * q + 1] = w.y * S[4 * q + 1] + k.y * vj;
-              o0 += r.z * (S[4 * q + 2] + u.z * vj);
-              S[4 * q + 2] = w.z * S[4 * q + 2] + k.z * vj;
-              o1 += r.w * (S[4 * q + 3] + u.w * vj);
-              S[4 * q + 3] = w.w * S[4 * q + 3] + k.w * vj;
+#pragma unroll
+              for (int c2 = 0; c2 < CPT; ++c2) {
+                float* Sc = S[c2];
+                o0[c2] += r.x * (Sc[4 * q] + u.x * vj[c2]);
+                Sc[4 * q] = w.x * Sc[4 * q] + k.x * vj[c2];
+                o1[c2] += r.y * (Sc[4 * q + 1] + u.y * vj[c2]);
+                Sc[4 * q + 1] = w.y * Sc[4 * q + 1] + k.y * vj[c2];
+                o0[c2] += r.z * (Sc[4 * q + 2] + u.z * vj[c2]);
+                Sc[4 * q + 2] = w.z * Sc[4 * q + 2] + k.z * vj[c2];
+                o1[c2] += r.w * (Sc[4 * q + 3] + u.w * vj[c2]);
+                Sc[4 * q + 3] = w.w * Sc[4 * q + 3] + k.w * vj[c2];
+              }
             }
           }
-          float o = o0 + o1;
-          for (int off = 1; off < KL; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-          if (on && slice == 0) o_c[t * N + col] = o;
+#pragma unroll
+          for (int c2 = 0; c2 < CPT; ++c2) {
+            float o = o0[c2] + o1[c2];
+            for (int off = 1; off < KL; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+            if (on[c2] && slice == 0) o_c[t * N + col0 + c2] = o;
+          }
         }
       }
     } else {
@@ -339,8 +368,10 @@ __global__ void __launch_bounds__(MAXT, 1) recurrence_kernel(ScanArgs a, int KL,
     __syncthreads();
   }
 #pragma unroll
-  for (int i = 0; i < NPT; ++i)
-    if (on && key0 + i < N) st[(size_t)(key0 + i) * N + col] = S[i];
+  for (int c2 = 0; c2 < CPT; ++c2)
+#pragma unroll
+    for (int i = 0; i < NPT; ++i)
+      if (on[c2] && key0 + i < N) st[(size_t)(key0 + i) * N + col0 + c2] = S[c2][i];
   if (a.last_rows && head == 0 && T_len > 0) {
     const T* last = reinterpret_cast<const T*>(a.last_rows) + (size_t)(row0 + T_len - 1) * a.last_stride;
     float* dst = a.last_state + (size_t)slot * a.C;
@@ -348,24 +379,24 @@ __global__ void __launch_bounds__(MAXT, 1) recurrence_kernel(ScanArgs a, int KL,
   }
 }
 
-template <typename T, int RULE, int NPT, int TC, int MAXT>
+template <typename T, int RULE, int NPT, int TC, int PROD, int MAXT>
 int launch_recurrence(const ScanArgs& a, cudaStream_t stream) {
   int KL = 1;
   while (KL * NPT < a.N) KL <<= 1;
-  const int cons = ((a.N * KL + 31) / 32) * 32;
+  const int cons = (((a.N + CPT - 1) / CPT * KL + 31) / 32) * 32;
   if (cons + PROD > MAXT) return -2;
   const size_t buf = (size_t)5 * TC * KL * (NPT + 4) + (size_t)TC * a.N;
   const size_t smem = (2 * buf + (size_t)2 * TC * a.N + (size_t)a.R * a.N + (size_t)TC * a.R + 2 * TC) * sizeof(float);
   if (smem > 220 * 1024) return -2;
-  auto kern = recurrence_kernel<T, RULE, NPT, TC, MAXT>;
+  auto kern = recurrence_kernel<T, RULE, NPT, TC, PROD, MAXT>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   return (int)launch_pdl(kern, dim3(a.n_seqs * a.H), dim3(cons + PROD), smem, stream, a, KL, cons);
 }
 
 template <typename T, int RULE>
 int pick_recurrence(const ScanArgs& a, cudaStream_t stream) {
-  if (a.N <= 64) return launch_recurrence<T, RULE, 16, 32, 256 + PROD>(a, stream);
-  if (a.N <= 128) return launch_recurrence<T, RULE, 32, 16, 512 + PROD>(a, stream);
+  if (a.N <= 64) return launch_recurrence<T, RULE, 16, 32, 256, 384>(a, stream);
+  if (a.N <= 128) return launch_recurrence<T, RULE, 32, 16, 128, 384>(a, stream);
   return -2;  // a head's state no longer fits the registers of one block
 }
 

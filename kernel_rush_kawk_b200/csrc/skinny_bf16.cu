@@ -1,6 +1,6 @@
 // Decode-time matrix product for few rows: out[M, N] = act(x)[M, K] * W[N, K]^T,
 // bfloat16, M <= 16, with the residual add and RMSNorm folded into the prologue
-// and SwiGLU into the epilogue.
+// and SwiGLU (or the gated tanh-GELU of models that compute it in float32) into the epilogue.
 //
 // At decode the projections are pure weight streaming (the reference says so of
 // its own skinny kernel, engine/kernels/gemm.py:1-10 of willzeng274/kernel-rush-kawk).
@@ -56,7 +56,7 @@ __host__ __device__ constexpr int ring_loads() {
 // ring-full of copies is issued before anything else (before the wait on the
 // previous kernel, before the norm prologue), so the memory system is busy from the
 // block's first instruction.
-template <int WARPS, int NT, int RT, bool SWIGLU, bool NORM, typename TOut, bool DEEP = false, int KSPLIT = 1, int RING = 0>
+template <int WARPS, int NT, int RT, int SWIGLU, bool NORM, typename TOut, bool DEEP = false, int KSPLIT = 1, int RING = 0>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __restrict__ W,
               const bf16* __restrict__ branch, const void* __restrict__ gain, int gain_f32, bf16* __restrict__ x_new,
@@ -303,7 +303,9 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
     }
     const int n = n0 + f;
     if (m < M && n < N) {
-      if (SWIGLU) {
+      if (SWIGLU == 2) {  // tanh form of GELU on the gate, gate and up as accumulated (float32), rounded once
+        v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v))) * v2;
+      } else if (SWIGLU) {
         const float gate = round_to<bf16>(v), up = round_to<bf16>(v2);
         v = round_to<bf16>(gate / (1.0f + expf(-gate))) * up;
       }
@@ -313,7 +315,7 @@ skinny_kernel(TOut* __restrict__ out, const bf16* __restrict__ x, const bf16* __
   KRK_TRACE_END(K)
 }
 
-template <int WARPS, int NT, int RT, bool SWIGLU, bool NORM, typename TOut, bool DEEP = false, int KSPLIT = 1, int RING = 0>
+template <int WARPS, int NT, int RT, int SWIGLU, bool NORM, typename TOut, bool DEEP = false, int KSPLIT = 1, int RING = 0>
 int launch_warps(void* out, const void* x, const void* W, const void* branch, const void* gain, int gain_f32, void* x_new, int M,
            int N, int K, float eps, cudaStream_t stream) {
   constexpr int THREADS = WARPS * 32;
@@ -363,7 +365,7 @@ int launch_warps(void* out, const void* x, const void* W, const void* branch, co
 // Blocks of 8 warps hold more bytes in flight each; blocks of 4 warps are small enough for
 // five of them to share an SM. With between two and five blocks per SM the small ones all
 // fit at once (one wave, no straggling second wave of a few blocks); otherwise the large.
-template <int NT, int RT, bool SWIGLU, bool NORM, typename TOut>
+template <int NT, int RT, int SWIGLU, bool NORM, typename TOut>
 int launch(void* out, const void* x, const void* W, const void* branch, const void* gain, int gain_f32, void* x_new, int M,
            int N, int K, float eps, cudaStream_t stream) {
   const int blocks = (N + 16 * RT - 1) / (16 * RT);
@@ -391,7 +393,7 @@ int launch(void* out, const void* x, const void* W, const void* branch, const vo
   return launch_warps<8, NT, RT, SWIGLU, NORM, TOut>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
 }
 
-template <int NT, bool SWIGLU, bool NORM, typename TOut>
+template <int NT, int SWIGLU, bool NORM, typename TOut>
 int pick_rt(void* out, const void* x, const void* W, const void* branch, const void* gain, int gain_f32, void* x_new,
             int M, int N, int K, float eps, cudaStream_t stream) {
   // two row tiles per block when that still leaves a few blocks for each of the 148 SMs
@@ -400,7 +402,7 @@ int pick_rt(void* out, const void* x, const void* W, const void* branch, const v
   return launch<NT, 1, SWIGLU, NORM, TOut>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
 }
 
-template <bool SWIGLU, bool NORM, typename TOut>
+template <int SWIGLU, bool NORM, typename TOut>
 int pick_nt(void* out, const void* x, const void* W, const void* branch, const void* gain, int gain_f32, void* x_new,
             int M, int N, int K, float eps, cudaStream_t stream) {
   if (M <= 8) return pick_rt<1, SWIGLU, NORM, TOut>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
@@ -432,14 +434,18 @@ KRK_API int krk_skinny_linear(void* out, const void* x, const void* W, const voi
   if (M > 16 || K % CHUNK || K <= 0) return -2;
   if (branch && !gain) return -2;
   const bool norm = gain != nullptr;
+  if (swiglu == 2) {  // gate and up with the tanh form of GELU; no norm prologue with it
+    if (out_dtype != KRK_DTYPE_BF16 || norm) return -4;
+    return pick_nt<2, false, bf16>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
+  }
   if (swiglu) {
     if (out_dtype != KRK_DTYPE_BF16) return -4;
-    return norm ? pick_nt<true, true, bf16>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream)
-                : pick_nt<true, false, bf16>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
+    return norm ? pick_nt<1, true, bf16>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream)
+                : pick_nt<1, false, bf16>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
   }
   if (out_dtype == KRK_DTYPE_F32)
-    return norm ? pick_nt<false, true, float>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream)
-                : pick_nt<false, false, float>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
-  return norm ? pick_nt<false, true, bf16>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream)
-              : pick_nt<false, false, bf16>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
+    return norm ? pick_nt<0, true, float>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream)
+                : pick_nt<0, false, float>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
+  return norm ? pick_nt<0, true, bf16>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream)
+              : pick_nt<0, false, bf16>(out, x, W, branch, gain, gain_f32, x_new, M, N, K, eps, stream);
 }
