@@ -60,7 +60,7 @@ _MIX_SIGNATURES = {
     "krk_sink_attention": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P,
                            c_int, _P, _P, c_int, c_float, c_int, c_int, _P],
     "krk_sink_attention_single": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
-                                  c_int, _P, _P, c_int, c_float, c_int, c_int, _P],
+                                  c_int, _P, _P, c_int, c_float, c_int, c_int, _P, c_int, _P],
     "krk_token_shift": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P],
     "krk_linear_recurrence": [c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, _P, _P, _P, _P,
                               _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int,
@@ -515,11 +515,20 @@ class Kernels:
         if batch.is_decode and proj.shape[0] == batch.n_seqs:
             # one token per sequence: a block per (sequence, kv head), its warps splitting the window's keys. The
             # choice depends on the step's shape alone, so a sequence's results do not depend on its batch
+            # blocks per (sequence, kv head) by the number of such items alone, never by lengths, so that a
+            # captured step stays valid: enough to give every SM a block while items are few
+            items = batch.n_seqs * cache.kv_heads
+            splits = 8 if items <= 18 else 4 if items <= 37 else 2 if items <= 74 else 1
+            key = ("sink", batch.n_seqs, heads, vdim, splits)
+            scratch = self._partials.get(key)
+            if scratch is None and splits > 1:
+                scratch = self._partials[key] = torch.empty(batch.n_seqs * heads * splits * (vdim + 2),
+                                                            dtype=torch.float32, device=self.device)
             rc = self.mix.krk_sink_attention_single(
                 optr, ostride, out_col, float(out_scale), ptr, stride, q_col, heads, cache.kv_heads, dim, vdim,
                 _ptr(sink), batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), cache.table.data_ptr(), cache.width,
-                cache.k.data_ptr(), cache.v.data_ptr(), batch.n_seqs, float(scale), int(window or 0), _code(proj.dtype),
-                self._stream())
+                cache.k.data_ptr(), cache.v.data_ptr(), batch.n_seqs, float(scale), int(window or 0), splits,
+                _ptr(scratch), _code(proj.dtype), self._stream())
             if rc != -2:  # -2: heads too large for it; the general kernel takes them
                 self._ok(rc, "single-token windowed attention with a sink")
                 return

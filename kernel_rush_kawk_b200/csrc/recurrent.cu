@@ -122,7 +122,8 @@ __global__ void __launch_bounds__(MAXT, 1) recurrence_kernel(ScanArgs a, int KL,
     const int m = i / N, c = i % N;
     w2_s[i] = to_float<T>(reinterpret_cast<const T*>(a.w2)[(size_t)(ch0 + c) * R + m]);
   }
-  for (int i = tid; i < 2 * BUF; i += blockDim.x) sm[i] = 0.f;
+  if (KL * NPT != N)  // the lanes' slices reach past the head's channels: those places stay zero for the whole pass
+    for (int i = tid; i < 2 * BUF; i += blockDim.x) sm[i] = 0.f;
   grid_dependency_wait();
   const int row0 = a.cu_q[seq], T_len = a.seq_qlen[seq], slot = a.seq_slot[seq];
   const int n_chunks = (T_len + TC - 1) / TC;

@@ -20,7 +20,8 @@
 // Its warps take the window's 32-key chunks in turn, each lane scores its key against every query head
 // of the group from one read of the key (and every value row serves all of the group's heads), and the
 // warps' running (maximum, sum, output) are merged in warp order at the end; the sink enters once, as
-// the first warp's starting state.
+// the first warp's starting state. Where few (sequence, kv head) items would leave most SMs idle, several
+// blocks share an item's chunks and a small kernel merges their results in block order.
 #include "common.cuh"
 
 namespace {
@@ -189,7 +190,7 @@ __global__ void sink_attention_kernel(T* __restrict__ out, int out_stride, int o
 }
 
 constexpr int GROUP_MAX = 8;       // query heads of one kv head that a block serves at once
-constexpr int SINGLE_WARPS = 16;
+constexpr int SINGLE_WARPS = 8;
 
 template <typename T> __device__ __forceinline__ void load8(const T* p, float* f);
 template <> __device__ __forceinline__ void load8<float>(const float* p, float* f) {
@@ -225,14 +226,15 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
                              const float* __restrict__ sink, const int* __restrict__ seq_slot,
                              const int* __restrict__ seq_start, const int* __restrict__ table, int width,
                              const T* __restrict__ k_cache, const T* __restrict__ v_cache, float scale, int window,
-                             int g0, int GN) {
+                             int g0, int GN, int SPL, float* __restrict__ scratch) {
   extern __shared__ __align__(16) float sm1[];
   float* q_s = sm1;                       // [GN][D]
   float* part = q_s + GN * D;             // [warps][GN][DV + 2]
   grid_launch_dependents();
   grid_dependency_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int seq = blockIdx.x / HKV, kh = blockIdx.x % HKV;
+  const int split = blockIdx.x % SPL, item = blockIdx.x / SPL;  // the block takes every SPL-th chunk of its item
+  const int seq = item / HKV, kh = item % HKV;
   const int G = HQ / HKV;
   const int head0 = kh * G + g0;          // the block's first query head
   const int pos = seq_start[seq];         // the one new token sits at the sequence's length before the step
@@ -245,14 +247,14 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
   float m[GROUP_MAX], l[GROUP_MAX], acc[GROUP_MAX][MAX_V_PER_LANE / 2];
 #pragma unroll
   for (int g = 0; g < GROUP_MAX; ++g) {
-    const bool has = warp == 0 && sink != nullptr && g < GN;
+    const bool has = warp == 0 && split == 0 && sink != nullptr && g < GN;
     m[g] = has ? sink[head0 + g] : -INFINITY;
     l[g] = has ? 1.f : 0.f;
 #pragma unroll
     for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) acc[g][i] = 0.f;
   }
   const bool vec = (D & 7) == 0;  // rows of the cache then start on 16-byte boundaries (32 for float)
-  for (int base = first + 32 * warp; base <= pos; base += 32 * SINGLE_WARPS) {
+  for (int base = first + 32 * (split + SPL * warp); base <= pos; base += 32 * SPL * SINGLE_WARPS) {
     const int key = base + lane;
     float s[GROUP_MAX];
 #pragma unroll
@@ -262,15 +264,15 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
       my_page = page_of(table, width, slot, key);
       const T* kp = k_cache + (((size_t)my_page * HKV + kh) * KRK_PAGE + (key % KRK_PAGE)) * D;
       if (vec) {
-        // 32 elements of the key row are requested at once (a row is a lane's own, nothing shares its
+        // 64 elements of the key row are requested at once (a row is a lane's own, nothing shares its
         // latency), then multiplied with every head's query
         int d = 0;
-        for (; d + 32 <= D; d += 32) {
-          float kf[4][8];
+        for (; d + 64 <= D; d += 64) {
+          float kf[8][8];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) load8<T>(kp + d + 8 * c, kf[c]);
+          for (int c = 0; c < 8; ++c) load8<T>(kp + d + 8 * c, kf[c]);
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 8; ++c)
 #pragma unroll
             for (int g = 0; g < GROUP_MAX; ++g)
               if (g < GN) {
@@ -315,10 +317,10 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
       m[g] = m_new;
     }
     const int n = min(32, pos - base + 1);
-    for (int j0 = 0; j0 < n; j0 += 8) {  // eight value rows are requested before the first is used
-      float vf[8][MAX_V_PER_LANE / 2];
+    for (int j0 = 0; j0 < n; j0 += 16) {  // sixteen value rows are requested before the first is used
+      float vf[16][MAX_V_PER_LANE / 2];
 #pragma unroll
-      for (int jj = 0; jj < 8; ++jj) {
+      for (int jj = 0; jj < 16; ++jj) {
         const int j = j0 + jj;
         const int kj = base + j;
         const int page = __shfl_sync(0xffffffffu, my_page, j & 31);  // lane j looked its key's page up already
@@ -334,7 +336,7 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
         }
       }
 #pragma unroll
-      for (int jj = 0; jj < 8; ++jj)
+      for (int jj = 0; jj < 16; ++jj)
 #pragma unroll
         for (int g = 0; g < GROUP_MAX; ++g) {
           if (g >= GN) continue;
@@ -374,6 +376,16 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
         if (d < DV) o[i] += src[d] * f;
       }
     }
+    if (SPL > 1) {  // this block's share of the keys: (maximum, sum, output) for the merge kernel
+      float* dst = scratch + (((size_t)item * SPL + split) * G + g0 + g) * PS;
+      if (lane == 0) { dst[DV] = mx; dst[DV + 1] = total; }
+#pragma unroll
+      for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) {
+        const int d = V4 ? 4 * lane + i : lane + 32 * i;
+        if (d < DV) dst[d] = o[i];
+      }
+      continue;
+    }
     T* op = out + (size_t)seq * out_stride + out_col + (size_t)(head0 + g) * DV;
     const float inv = out_scale / total;
 #pragma unroll
@@ -381,6 +393,43 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
       const int d = V4 ? 4 * lane + i : lane + 32 * i;
       if (d < DV) op[d] = from_float<T>(o[i] * inv);
     }
+  }
+}
+
+// The blocks' shares of one (sequence, head), merged in block order: one warp each.
+template <typename T>
+__global__ void sink_attention_merge_kernel(T* __restrict__ out, int out_stride, int out_col, float out_scale,
+                                            const float* __restrict__ scratch, int HQ, int HKV, int DV, int SPL,
+                                            int n_items) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31;
+  const int G = HQ / HKV, PS = DV + 2;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)n_items * G) return;
+  const int item = (int)(w / G), g = (int)(w % G);
+  const int seq = item / HKV, kh = item % HKV;
+  float mx = -INFINITY;
+  for (int sp = 0; sp < SPL; ++sp) mx = fmaxf(mx, scratch[(((size_t)item * SPL + sp) * G + g) * PS + DV]);
+  float total = 0.f, o[MAX_V_PER_LANE];
+#pragma unroll
+  for (int i = 0; i < MAX_V_PER_LANE; ++i) o[i] = 0.f;
+  for (int sp = 0; sp < SPL; ++sp) {
+    const float* src = scratch + (((size_t)item * SPL + sp) * G + g) * PS;
+    const float f = src[DV] == -INFINITY ? 0.f : expf(src[DV] - mx);
+    total += src[DV + 1] * f;
+#pragma unroll
+    for (int i = 0; i < MAX_V_PER_LANE; ++i) {
+      const int d = lane + 32 * i;
+      if (d < DV) o[i] += src[d] * f;
+    }
+  }
+  T* op = out + (size_t)seq * out_stride + out_col + (size_t)(kh * G + g) * DV;
+  const float inv = out_scale / total;
+#pragma unroll
+  for (int i = 0; i < MAX_V_PER_LANE; ++i) {
+    const int d = lane + 32 * i;
+    if (d < DV) op[d] = from_float<T>(o[i] * inv);
   }
 }
 
@@ -427,15 +476,17 @@ KRK_API int krk_sink_attention(void* out, int out_stride, int out_col, float out
 }
 
 // One token per sequence: rows are the sequences, in order. Value heads of up to 128 elements; others take
-// krk_sink_attention.
+// krk_sink_attention. splits > 1: that many blocks share an item's keys and a merge kernel follows; scratch then
+// holds n_seqs * HQ * splits * (DV + 2) floats.
 KRK_API int krk_sink_attention_single(void* out, int out_stride, int out_col, float out_scale, const void* proj, int stride,
                                       int q_col, int HQ, int HKV, int D, int DV, const float* sink, const int* seq_slot,
                                       const int* seq_start, const int* table, int width, const void* k_cache,
-                                      const void* v_cache, int n_seqs, float scale, int window, int dtype,
-                                      cudaStream_t stream) {
+                                      const void* v_cache, int n_seqs, float scale, int window, int splits,
+                                      float* scratch, int dtype, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (DV > 32 * (MAX_V_PER_LANE / 2) || D > 1024) return -2;
   const int G = HQ / HKV;
+  const int SPL = (splits > 1 && scratch) ? splits : 1;
   for (int g0 = 0; g0 < G; g0 += GROUP_MAX) {
     const int GN = min(GROUP_MAX, G - g0);
     const size_t smem = ((size_t)GN * D + (size_t)SINGLE_WARPS * GN * (DV + 2)) * sizeof(float);
@@ -450,14 +501,26 @@ KRK_API int krk_sink_attention_single(void* out, int out_stride, int out_col, fl
     }
     if (dtype == KRK_DTYPE_F32)
       e = launch_pdl(v4 ? sink_attention_single_kernel<float, true> : sink_attention_single_kernel<float, false>,
-                     dim3(n_seqs * HKV), dim3(SINGLE_WARPS * 32), smem, stream,
+                     dim3(n_seqs * HKV * SPL), dim3(SINGLE_WARPS * 32), smem, stream,
                      (float*)out, out_stride, out_col, out_scale, (const float*)proj, stride, q_col, HQ, HKV, D, DV, sink,
-                     seq_slot, seq_start, table, width, (const float*)k_cache, (const float*)v_cache, scale, window, g0, GN);
+                     seq_slot, seq_start, table, width, (const float*)k_cache, (const float*)v_cache, scale, window, g0, GN, SPL, scratch);
     else
       e = launch_pdl(v4 ? sink_attention_single_kernel<bf16, true> : sink_attention_single_kernel<bf16, false>,
-                     dim3(n_seqs * HKV), dim3(SINGLE_WARPS * 32), smem, stream,
+                     dim3(n_seqs * HKV * SPL), dim3(SINGLE_WARPS * 32), smem, stream,
                      (bf16*)out, out_stride, out_col, out_scale, (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink,
-                     seq_slot, seq_start, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale, window, g0, GN);
+                     seq_slot, seq_start, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale, window, g0, GN, SPL, scratch);
+    if (e != cudaSuccess) return (int)e;
+  }
+  if (SPL > 1) {
+    const long long warps = (long long)n_seqs * HKV * G;
+    const unsigned blocks = (unsigned)((warps + 3) / 4);
+    cudaError_t e;
+    if (dtype == KRK_DTYPE_F32)
+      e = launch_pdl(sink_attention_merge_kernel<float>, dim3(blocks), dim3(128), 0, stream, (float*)out, out_stride,
+                     out_col, out_scale, (const float*)scratch, HQ, HKV, DV, SPL, n_seqs * HKV);
+    else
+      e = launch_pdl(sink_attention_merge_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, (bf16*)out, out_stride,
+                     out_col, out_scale, (const float*)scratch, HQ, HKV, DV, SPL, n_seqs * HKV);
     if (e != cudaSuccess) return (int)e;
   }
   return 0;
