@@ -37,7 +37,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     p.add_argument("--out", required=True, help="folder that receives <step>.f32")
     p.add_argument("--max-tokens", type=int, required=True,
-                   help="most tokens live requests hold at any time, each request rounded up to a multiple of 64")
+                   help="most tokens live requests hold at any time (room for each request's partly filled last page is added)")
     p.add_argument("--no-graphs", action="store_true", help="run decode steps without CUDA graphs")
     return p
 
@@ -50,7 +50,11 @@ def run(args, stdin=None, stdout=None) -> int:
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
     pages = max(1, -(-args.max_tokens // PAGE))
-    engine = Engine(args.model, dtype=args.dtype, max_tokens=pages * PAGE, max_slots=min(pages, 4096),
+    # --max-tokens counts tokens; the cache hands out whole pages, and every live request leaves part of its last
+    # page unused: room for that beside the counted tokens (a page per request, for up to 256 requests or as many
+    # as there are pages)
+    slack = min(pages, 256)
+    engine = Engine(args.model, dtype=args.dtype, max_tokens=(pages + slack) * PAGE, max_slots=min(pages, 4096),
                     max_context=pages * PAGE, use_cuda_graphs=not args.no_graphs)
     slots: dict[str, int] = {}
     for line in stdin:

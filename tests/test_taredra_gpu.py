@@ -29,7 +29,7 @@ def runtime(dtype):
 
     # with the per-head-size attention libraries of the sizes below loaded, bfloat16 steps of many tokens whose key
     # and value heads have one of these sizes take the tensor-core kernel; all others the general one
-    return Runtime(torch.device("cuda:0"), dtype, load_kernels((16, 32, 64)))
+    return Runtime(torch.device("cuda:0"), dtype, load_kernels((16, 32, 48, 64)))
 
 
 def rand(shape, seed, scale=1.0):
@@ -140,6 +140,8 @@ ATTN_SHAPES = [  # hidden, heads, kv_heads, dim, vdim, window, rot, base
     (40, 2, 2, 24, 8, 7, 24, 50.0),
     (48, 3, 1, 8, 40, 130, 2, 10.0),
     (64, 2, 1, 64, 64, 1, 64, 1e4),
+    (96, 4, 2, 48, 48, 40, 32, 1e4),
+    (40, 10, 1, 8, 8, 90, 4, 30.0),
 ]
 
 
@@ -234,7 +236,8 @@ def test_one_key_at_the_windows_edge(dtype, window, spike_at, T):
         close(torch.cat(outs), want, dtype, f"window {window}, key at {spike_at}, pieces {pieces[:3]}")
 
 
-STATE_SHAPES = [(64, 3, 16, 8), (48, 1, 48, 16), (96, 2, 32, 5), (64, 1, 64, 16), (40, 5, 8, 3), (64, 1, 128, 4)]
+STATE_SHAPES = [(64, 3, 16, 8), (48, 1, 48, 16), (96, 2, 32, 5), (64, 1, 64, 16), (40, 5, 8, 3), (64, 1, 128, 4),
+                (40, 2, 20, 3), (30, 2, 5, 2), (72, 1, 100, 40)]
 
 
 def state_weights(kind, C, H, N, R, seed):
@@ -461,3 +464,25 @@ def test_greedy_generation_through_the_engine(folders, dtype):
             allowed = (1e-4 if dtype == "float32" else 5e-2) * (ref - ref.mean()).pow(2).mean().sqrt().item()
             assert ref.max().item() - ref[tok].item() <= allowed, f"request {i} step {t}: token {tok} is not the plain choice"
             seq.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_program(folders, dtype, tmp_path):
+    """bin/trace_run on a model folder of this design: requests alone, decoded, and unequal requests in one batch
+    that shrinks as they end, with --max-tokens counting tokens only (no rounding to pages)."""
+    from test_replay_gpu import Trace, run_trace
+
+    name = "ta"
+    vocab = CONFIGS[name]["vocab"]
+    seqs = prompts(name, [1, 97, 130, 45], seed=17)
+    trace = Trace()
+    for i, toks in enumerate(seqs):
+        trace.batch({f"r{i}w": toks}, [len(toks)])
+    trace.batch({"r1d": seqs[1]}, [len(seqs[1]) - 40])
+    trace.batch({"r0b": seqs[0], "r1b": seqs[1], "r2b": seqs[2], "r3b": seqs[3]}, [1, 65, 98, 13])
+    got = run_trace(folders[name], dtype, trace, tmp_path / "out", sum(len(s) for s in seqs), vocab)
+    assert len(got) >= sum(len(s) for s in seqs)
+    for (rid, pos), rows in got.items():
+        ref = plain_logits(folders[name], seqs[int(rid[1])])[pos:pos + 1]
+        for row in rows:
+            assert_logits(row[None], ref, dtype, f"{dtype} request {rid} position {pos}")
