@@ -64,7 +64,7 @@ _MIX_SIGNATURES = {
     "krk_token_shift": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P],
     "krk_linear_recurrence": [c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, _P, _P, _P, _P,
                               _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int,
-                              c_int, _P, _P, _P, c_int, _P],
+                              c_int, _P, _P, _P, c_int, _P, _P, c_int, _P],
 }
 _ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "sigmoid": 2}
 _ATTN_SIGNATURES = {
@@ -131,6 +131,9 @@ class Kernels:
         # tokens: 4.08 against 3.14 ms), where a block's own pace, not the bytes in flight, is the bound.
         self.tma_decode_splits = {1, 2}
         self.use_tuned_library_gemm = hasattr(self.core, "krk_lt_gemm_bf16")
+        # steps of many tokens: prepare / scan / finish kernels instead of the fused one. Bit-equal to it and, on one
+        # prompt, no faster (the scan itself bounds both), so it is off; it needs rows * channels * 28 bytes of scratch
+        self.split_recurrence = False
         self.launches = 0
 
     def _attn_lib(self, head_dim: int) -> ctypes.CDLL:
@@ -572,13 +575,19 @@ class Kernels:
             (last_ptr, last_stride), C, last_state = self._rows_view(last_rows[0]), last_rows[0].shape[1], last_rows[1]
         if state.dtype != torch.float32 or not state.is_contiguous() or not w2.is_contiguous() or w2.dtype != r.dtype:
             raise KernelError("the recurrence keeps a contiguous float32 state and reads W2 in the path's dtype")
+        rows = r.shape[0]
+        prep = o_raw = None
+        if not batch.is_decode and dim % 4 == 0 and self.split_recurrence:
+            # steps of many tokens: decays and gates over all rows at once, the scan between them (float32 scratch)
+            prep = torch.empty(rows * heads * 6 * dim, dtype=torch.float32, device=r.device)
+            o_raw = torch.empty(rows * heads * dim, dtype=torch.float32, device=r.device)
         rc = self.mix.krk_linear_recurrence(
             {"wkv": 0, "delta": 1}[kind], views[0][0], views[0][1], views[1][0], views[1][1], views[2][0], views[2][1],
             views[3][0], views[3][1], rate_v[0], rate_v[1], lora_v[0], lora_v[1], w2.data_ptr(), w0.data_ptr(),
             _ptr(rate_bias), _ptr(bonus), norm_w.data_ptr(), state.data_ptr(), last_ptr, last_stride, C,
             _ptr(last_state), optr, ostride, out_col, float(out_scale), float(eps), float(decay_scale), heads, dim,
             lora.shape[1], batch.n_seqs, batch.cu_q.data_ptr(), batch.seq_qlen.data_ptr(), batch.seq_slot.data_ptr(),
-            _code(r.dtype), self._stream())
+            rows, _ptr(prep), _ptr(o_raw), _code(r.dtype), self._stream())
         self._ok(rc, f"{kind} recurrence (heads of up to 128 channels)")
 
     # -- token selection ------------------------------------------------------------

@@ -18,7 +18,7 @@
 // while one scans a chunk, the other computes the next chunk's decays, unit keys and rates into shared
 // memory (float32) and normalises, gates and stores the chunk before. A token's result is the same to
 // the bit however the sequence was cut into steps: the chunking regroups work, not sums.
-#include "common.cuh"
+#include "mma.cuh"  // cp.async
 
 namespace {
 
@@ -88,19 +88,93 @@ template <> __device__ __forceinline__ void store4_el<bf16>(bf16* p, const float
 
 __device__ __forceinline__ float sigmoidf(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-constexpr int CPT = 2;     // columns of S per scanning thread: every staged vector it reads serves both
+// CPT: columns of S per scanning thread (every staged vector it reads serves all of them).
+
+// One token's update of a thread's share of the state (CPT columns x NPT key channels) and its outputs,
+// summed over the KL lanes of a column. Both scan kernels run exactly this, so a token's result does not
+// depend on which of them served its step.
+template <int RULE, int NPT, int CPT>
+__device__ __forceinline__ void scan_token(float (&S)[CPT][NPT], const float4* r4, const float4* k4, const float4* w4,
+                                           const float4* u4, const float4* a4, const float (&vj)[CPT], int KL,
+                                           float (&o)[CPT]) {
+  float o0[CPT], o1[CPT];
+#pragma unroll
+  for (int c2 = 0; c2 < CPT; ++c2) o0[c2] = o1[c2] = 0.f;
+  if (RULE == 1) {
+    float s0[CPT], s1[CPT], uS[CPT];
+#pragma unroll
+    for (int c2 = 0; c2 < CPT; ++c2) s0[c2] = s1[c2] = 0.f;
+#pragma unroll
+    for (int q = 0; q < NPT / 4; ++q) {
+      const float4 u = u4[q];
+#pragma unroll
+      for (int c2 = 0; c2 < CPT; ++c2) {
+        s0[c2] += u.x * S[c2][4 * q];
+        s1[c2] += u.y * S[c2][4 * q + 1];
+        s0[c2] += u.z * S[c2][4 * q + 2];
+        s1[c2] += u.w * S[c2][4 * q + 3];
+      }
+    }
+#pragma unroll
+    for (int c2 = 0; c2 < CPT; ++c2) {
+      uS[c2] = s0[c2] + s1[c2];
+      for (int off = 1; off < KL; off <<= 1) uS[c2] += __shfl_xor_sync(0xffffffffu, uS[c2], off);
+    }
+#pragma unroll
+    for (int q = 0; q < NPT / 4; ++q) {
+      const float4 w = w4[q], au = a4[q], k = k4[q], r = r4[q];
+#pragma unroll
+      for (int c2 = 0; c2 < CPT; ++c2) {
+        float* Sc = S[c2];
+        Sc[4 * q] = w.x * Sc[4 * q] - au.x * uS[c2] + k.x * vj[c2];
+        o0[c2] += r.x * Sc[4 * q];
+        Sc[4 * q + 1] = w.y * Sc[4 * q + 1] - au.y * uS[c2] + k.y * vj[c2];
+        o1[c2] += r.y * Sc[4 * q + 1];
+        Sc[4 * q + 2] = w.z * Sc[4 * q + 2] - au.z * uS[c2] + k.z * vj[c2];
+        o0[c2] += r.z * Sc[4 * q + 2];
+        Sc[4 * q + 3] = w.w * Sc[4 * q + 3] - au.w * uS[c2] + k.w * vj[c2];
+        o1[c2] += r.w * Sc[4 * q + 3];
+      }
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < NPT / 4; ++q) {
+      const float4 w = w4[q], u = u4[q], k = k4[q], r = r4[q];
+#pragma unroll
+      for (int c2 = 0; c2 < CPT; ++c2) {
+        float* Sc = S[c2];
+        o0[c2] += r.x * (Sc[4 * q] + u.x * vj[c2]);
+        Sc[4 * q] = w.x * Sc[4 * q] + k.x * vj[c2];
+        o1[c2] += r.y * (Sc[4 * q + 1] + u.y * vj[c2]);
+        Sc[4 * q + 1] = w.y * Sc[4 * q + 1] + k.y * vj[c2];
+        o0[c2] += r.z * (Sc[4 * q + 2] + u.z * vj[c2]);
+        Sc[4 * q + 2] = w.z * Sc[4 * q + 2] + k.z * vj[c2];
+        o1[c2] += r.w * (Sc[4 * q + 3] + u.w * vj[c2]);
+        Sc[4 * q + 3] = w.w * Sc[4 * q + 3] + k.w * vj[c2];
+      }
+    }
+  }
+#pragma unroll
+  for (int c2 = 0; c2 < CPT; ++c2) {
+    o[c2] = o0[c2] + o1[c2];
+    for (int off = 1; off < KL; off <<= 1) o[c2] += __shfl_xor_sync(0xffffffffu, o[c2], off);
+  }
+}
 
 template <int PROD>
 __device__ __forceinline__ void producers_sync_n() { asm volatile("bar.sync 1, %0;" ::"n"(PROD) : "memory"); }
 
-// NPT: key channels of a column that one lane keeps (16 for heads of up to 64 channels, 32 up to 128).
+// NPT: key channels of a column that one lane keeps (16 for heads of up to 64 channels, 32 up to 128), CPT = 2
+// columns a thread. Lighter threads (8 channels, one column: four times the warps) were measured and are slower,
+// 0.83 against 0.60 us a token: every warp reads every staged vector, and shared-memory loads and the lanes'
+// exchanges, not issue slots, then bound the scan.
 // A lane's slice of a staged vector starts NPT + 4 floats after its neighbour's, so that the four
 // slices a quarter-warp reads at once fall into different banks. TC: tokens per chunk.
 //
 // The block's first `cons` threads scan; its last PROD threads (a multiple of 32) prepare the chunk after the one being
 // scanned (stage r, k, v; unit-key norms; decays and rates) into the other of two buffers and finish the
 // chunk before it (per-head norm, weight, gate, store). The two groups meet once per chunk.
-template <typename T, int RULE, int NPT, int TC, int PROD, int MAXT>
+template <typename T, int RULE, int NPT, int CPT, int TC, int PROD, int MAXT>
 __global__ void __launch_bounds__(MAXT, 1) recurrence_kernel(ScanArgs a, int KL, int cons) {
   constexpr int SL = NPT + 4;
   auto producers_sync = [] { producers_sync_n<PROD>(); };
@@ -167,73 +241,13 @@ __global__ void __launch_bounds__(MAXT, 1) recurrence_kernel(ScanArgs a, int KL,
           const float4* k4 = reinterpret_cast<const float4*>(buf + TC * VS + at);
           const float4* w4 = reinterpret_cast<const float4*>(buf + 2 * TC * VS + at);
           const float4* u4 = reinterpret_cast<const float4*>(buf + 3 * TC * VS + at);
-          float vj[CPT], o0[CPT], o1[CPT];
+          float vj[CPT], o[CPT];
 #pragma unroll
-          for (int c2 = 0; c2 < CPT; ++c2) {
-            vj[c2] = on[c2] ? v_s[t * N + col0 + c2] : 0.f;
-            o0[c2] = o1[c2] = 0.f;
-          }
-          if (RULE == 1) {
-            const float4* a4 = reinterpret_cast<const float4*>(buf + 4 * TC * VS + at);
-            float s0[CPT], s1[CPT], uS[CPT];
+          for (int c2 = 0; c2 < CPT; ++c2) vj[c2] = on[c2] ? v_s[t * N + col0 + c2] : 0.f;
+          scan_token<RULE, NPT, CPT>(S, r4, k4, w4, u4, reinterpret_cast<const float4*>(buf + 4 * TC * VS + at), vj, KL, o);
 #pragma unroll
-            for (int c2 = 0; c2 < CPT; ++c2) s0[c2] = s1[c2] = 0.f;
-#pragma unroll
-            for (int q = 0; q < NPT / 4; ++q) {
-              const float4 u = u4[q];
-#pragma unroll
-              for (int c2 = 0; c2 < CPT; ++c2) {
-                s0[c2] += u.x * S[c2][4 * q];
-                s1[c2] += u.y * S[c2][4 * q + 1];
-                s0[c2] += u.z * S[c2][4 * q + 2];
-                s1[c2] += u.w * S[c2][4 * q + 3];
-              }
-            }
-#pragma unroll
-            for (int c2 = 0; c2 < CPT; ++c2) {
-              uS[c2] = s0[c2] + s1[c2];
-              for (int off = 1; off < KL; off <<= 1) uS[c2] += __shfl_xor_sync(0xffffffffu, uS[c2], off);
-            }
-#pragma unroll
-            for (int q = 0; q < NPT / 4; ++q) {
-              const float4 w = w4[q], au = a4[q], k = k4[q], r = r4[q];
-#pragma unroll
-              for (int c2 = 0; c2 < CPT; ++c2) {
-                float* Sc = S[c2];
-                Sc[4 * q] = w.x * Sc[4 * q] - au.x * uS[c2] + k.x * vj[c2];
-                o0[c2] += r.x * Sc[4 * q];
-                Sc[4 * q + 1] = w.y * Sc[4 * q + 1] - au.y * uS[c2] + k.y * vj[c2];
-                o1[c2] += r.y * Sc[4 * q + 1];
-                Sc[4 * q + 2] = w.z * Sc[4 * q + 2] - au.z * uS[c2] + k.z * vj[c2];
-                o0[c2] += r.z * Sc[4 * q + 2];
-                Sc[4 * q + 3] = w.w * Sc[4 * q + 3] - au.w * uS[c2] + k.w * vj[c2];
-                o1[c2] += r.w * Sc[4 * q + 3];
-              }
-            }
-          } else {
-#pragma unroll
-            for (int q = 0; q < NPT / 4; ++q) {
-              const float4 w = w4[q], u = u4[q], k = k4[q], r = r4[q];
-#pragma unroll
-              for (int c2 = 0; c2 < CPT; ++c2) {
-                float* Sc = S[c2];
-                o0[c2] += r.x * (Sc[4 * q] + u.x * vj[c2]);
-                Sc[4 * q] = w.x * Sc[4 * q] + k.x * vj[c2];
-                o1[c2] += r.y * (Sc[4 * q + 1] + u.y * vj[c2]);
-                Sc[4 * q + 1] = w.y * Sc[4 * q + 1] + k.y * vj[c2];
-                o0[c2] += r.z * (Sc[4 * q + 2] + u.z * vj[c2]);
-                Sc[4 * q + 2] = w.z * Sc[4 * q + 2] + k.z * vj[c2];
-                o1[c2] += r.w * (Sc[4 * q + 3] + u.w * vj[c2]);
-                Sc[4 * q + 3] = w.w * Sc[4 * q + 3] + k.w * vj[c2];
-              }
-            }
-          }
-#pragma unroll
-          for (int c2 = 0; c2 < CPT; ++c2) {
-            float o = o0[c2] + o1[c2];
-            for (int off = 1; off < KL; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-            if (on[c2] && slice == 0) o_c[t * N + col0 + c2] = o;
-          }
+          for (int c2 = 0; c2 < CPT; ++c2)
+            if (on[c2] && slice == 0) o_c[t * N + col0 + c2] = o[c2];
         }
       }
     } else {
@@ -380,7 +394,7 @@ __global__ void __launch_bounds__(MAXT, 1) recurrence_kernel(ScanArgs a, int KL,
   }
 }
 
-template <typename T, int RULE, int NPT, int TC, int PROD, int MAXT>
+template <typename T, int RULE, int NPT, int CPT, int TC, int PROD, int MAXT>
 int launch_recurrence(const ScanArgs& a, cudaStream_t stream) {
   int KL = 1;
   while (KL * NPT < a.N) KL <<= 1;
@@ -389,16 +403,204 @@ int launch_recurrence(const ScanArgs& a, cudaStream_t stream) {
   const size_t buf = (size_t)5 * TC * KL * (NPT + 4) + (size_t)TC * a.N;
   const size_t smem = (2 * buf + (size_t)2 * TC * a.N + (size_t)a.R * a.N + (size_t)TC * a.R + 2 * TC) * sizeof(float);
   if (smem > 220 * 1024) return -2;
-  auto kern = recurrence_kernel<T, RULE, NPT, TC, PROD, MAXT>;
+  auto kern = recurrence_kernel<T, RULE, NPT, CPT, TC, PROD, MAXT>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   return (int)launch_pdl(kern, dim3(a.n_seqs * a.H), dim3(cons + PROD), smem, stream, a, KL, cons);
 }
 
 template <typename T, int RULE>
 int pick_recurrence(const ScanArgs& a, cudaStream_t stream) {
-  if (a.N <= 64) return launch_recurrence<T, RULE, 16, 32, 256, 384>(a, stream);
-  if (a.N <= 128) return launch_recurrence<T, RULE, 32, 16, 128, 384>(a, stream);
+  if (a.N <= 64) return launch_recurrence<T, RULE, 16, 2, 32, 256, 384>(a, stream);
+  if (a.N <= 128) return launch_recurrence<T, RULE, 32, 2, 16, 128, 384>(a, stream);
   return -2;  // a head's state no longer fits the registers of one block
+}
+
+// ---------------------------------------------------------------------------------------------------
+// An option for steps of many tokens per sequence (off by default: measured on 2,048 tokens of 8 heads of 64
+// channels it takes 1.15 ms with chunks of 32 tokens and 1.78 ms with chunks of 16, the fused kernel 1.24 ms
+// alone and 5 % less inside a prompt step): the same work as three kernels. What does not depend on the state
+// (decays, unit keys, rates; the per-head norm, weight and gate of the outputs) runs over all rows at
+// once on every SM; between them the scan kernel only streams the prepared float32 vectors into shared
+// memory with cp.async, one chunk ahead, and applies the rule. Every sum is the one the fused kernel
+// forms, in the same order, so the two agree to the bit.
+//   prep [rows, H, 6, N] float32: r, k, decay, u (or bonus * k), rate * u, v
+//   o    [rows, H * N]  float32: the raw outputs
+// ---------------------------------------------------------------------------------------------------
+template <typename T, int RULE>
+__global__ void recurrence_prepare_kernel(ScanArgs a, float* __restrict__ prep) {
+  extern __shared__ float sp[];  // [R] tanh of the low-rank input, then one float
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int N = a.N, R = a.R;
+  const size_t row = blockIdx.x;
+  const int head = blockIdx.y, ch0 = head * N;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const T* lp = reinterpret_cast<const T*>(a.lora);
+  for (int m = tid; m < R; m += blockDim.x) sp[m] = round_to<T>(tanhf(to_float<T>(lp[row * a.lora_stride + m])));
+  const T* kp = reinterpret_cast<const T*>(a.k) + row * a.k_stride + ch0;
+  if (RULE == 1 && tid < 32) {
+    float sq = 0.f;
+    for (int c = lane; c < N; c += 32) {
+      const float kv = to_float<T>(kp[c]);
+      sq += kv * kv;
+    }
+    sq = warp_sum(sq);
+    if (lane == 0) sp[R] = rsqrtf(sq + 1e-6f);
+  }
+  __syncthreads();
+  float* dst = prep + (row * a.H + head) * 6 * N;
+  const T* w2 = reinterpret_cast<const T*>(a.w2);
+  for (int c = tid; c < N; c += blockDim.x) {
+    const float kv = to_float<T>(kp[c]);
+    float z = 0.f;
+    for (int m = 0; m < R; ++m) z += sp[m] * to_float<T>(w2[(size_t)(ch0 + c) * R + m]);
+    z += a.w0[ch0 + c];
+    dst[c] = to_float<T>(reinterpret_cast<const T*>(a.r)[row * a.r_stride + ch0 + c]);
+    dst[N + c] = kv;
+    dst[5 * N + c] = to_float<T>(reinterpret_cast<const T*>(a.v)[row * a.v_stride + ch0 + c]);
+    if (RULE == 1) {
+      dst[2 * N + c] = expf(-a.decay_scale * sigmoidf(z));
+      const float u = kv * sp[R];
+      dst[3 * N + c] = u;
+      dst[4 * N + c] =
+          sigmoidf(to_float<T>(reinterpret_cast<const T*>(a.rate)[row * a.rate_stride + ch0 + c]) + a.rate_bias[ch0 + c]) * u;
+    } else {
+      dst[2 * N + c] = expf(-expf(z));
+      dst[3 * N + c] = a.bonus[ch0 + c] * kv;
+      dst[4 * N + c] = 0.f;
+    }
+  }
+}
+
+template <typename T, int RULE, int NPT, int CPT, int TC, int MAXT>
+__global__ void __launch_bounds__(MAXT)
+recurrence_scan_kernel(ScanArgs a, const float* __restrict__ prep, float* __restrict__ o_out, int KL) {
+  constexpr int SL = NPT + 4;
+  extern __shared__ __align__(16) float sm[];
+  const int N = a.N;
+  const int VS = KL * SL;
+  const int BUF = 5 * TC * VS + TC * N;
+  grid_launch_dependents();
+  const int seq = blockIdx.x / a.H, head = blockIdx.x % a.H;
+  const int tid = threadIdx.x;
+  if (KL * NPT != N)
+    for (int i = tid; i < 2 * BUF; i += blockDim.x) sm[i] = 0.f;
+  grid_dependency_wait();
+  const int row0 = a.cu_q[seq], T_len = a.seq_qlen[seq], slot = a.seq_slot[seq];
+  const int n_chunks = (T_len + TC - 1) / TC;
+  float* st = a.state + (((size_t)slot * a.H + head) * N) * N;
+  const int col0 = (tid / KL) * CPT, slice = tid % KL;
+  const int key0 = slice * NPT;
+  bool on[CPT];
+  float S[CPT][NPT];
+#pragma unroll
+  for (int c2 = 0; c2 < CPT; ++c2) {
+    on[c2] = col0 + c2 < N;
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) S[c2][i] = (on[c2] && key0 + i < N) ? st[(size_t)(key0 + i) * N + col0 + c2] : 0.f;
+  }
+  __syncthreads();
+  const int N4 = N / 4;
+  auto issue = [&](int c) {  // chunk c -> buffer c & 1, 16 bytes a request
+    const int nt = min(TC, T_len - c * TC);
+    float* buf = sm + (c & 1) * BUF;
+    for (int i = tid; i < nt * 6 * N4; i += blockDim.x) {
+      const int t = i / (6 * N4), rem = i % (6 * N4), vec = rem / N4, ch = 4 * (rem % N4);
+      const float* src = prep + (((size_t)(row0 + c * TC + t)) * a.H + head) * 6 * N + vec * N + ch;
+      float* dst = vec < 5 ? buf + vec * TC * VS + t * VS + (ch / NPT) * SL + (ch % NPT) : buf + 5 * TC * VS + t * N + ch;
+      cp_async_16(dst, src);
+    }
+    cp_async_commit();
+  };
+  if (n_chunks > 0) issue(0);
+  for (int c = 0; c < n_chunks; ++c) {
+    if (c + 1 < n_chunks) {
+      issue(c + 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int nt = min(TC, T_len - c * TC);
+    const float* buf = sm + (c & 1) * BUF;
+    const float* v_s = buf + 5 * TC * VS;
+    for (int t = 0; t < nt; ++t) {
+      const int at = t * VS + slice * SL;
+      float vj[CPT], o[CPT];
+#pragma unroll
+      for (int c2 = 0; c2 < CPT; ++c2) vj[c2] = on[c2] ? v_s[t * N + col0 + c2] : 0.f;
+      scan_token<RULE, NPT, CPT>(S, reinterpret_cast<const float4*>(buf + at), reinterpret_cast<const float4*>(buf + TC * VS + at),
+                            reinterpret_cast<const float4*>(buf + 2 * TC * VS + at),
+                            reinterpret_cast<const float4*>(buf + 3 * TC * VS + at),
+                            reinterpret_cast<const float4*>(buf + 4 * TC * VS + at), vj, KL, o);
+      float* orow = o_out + (size_t)(row0 + c * TC + t) * a.H * N + head * N;
+#pragma unroll
+      for (int c2 = 0; c2 < CPT; ++c2)
+        if (on[c2] && slice == 0) orow[col0 + c2] = o[c2];
+    }
+    __syncthreads();  // the buffer is free for the chunk after next
+  }
+#pragma unroll
+  for (int c2 = 0; c2 < CPT; ++c2)
+#pragma unroll
+    for (int i = 0; i < NPT; ++i)
+      if (on[c2] && key0 + i < N) st[(size_t)(key0 + i) * N + col0 + c2] = S[c2][i];
+  if (a.last_rows && head == 0 && T_len > 0) {
+    const T* last = reinterpret_cast<const T*>(a.last_rows) + (size_t)(row0 + T_len - 1) * a.last_stride;
+    float* dst = a.last_state + (size_t)slot * a.C;
+    for (int ch = tid; ch < a.C; ch += blockDim.x) dst[ch] = to_float<T>(last[ch]);
+  }
+}
+
+// out = o / sqrt(mean_head(o^2) + eps) * norm_w * gate(g) * out_scale: one warp per (row, head).
+template <typename T, int RULE>
+__global__ void recurrence_finish_kernel(ScanArgs a, const float* __restrict__ o_in, int rows) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int N = a.N, lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)rows * a.H) return;
+  const size_t row = (size_t)(w / a.H);
+  const int head = (int)(w % a.H), ch0 = head * N;
+  const float* o = o_in + row * a.H * N + ch0;
+  float sq = 0.f;
+  for (int c = lane; c < N; c += 32) sq += o[c] * o[c];
+  sq = warp_sum(sq);
+  const float rstd = rsqrtf(sq / (float)N + a.eps);
+  const T* gp = reinterpret_cast<const T*>(a.g) + row * a.g_stride + ch0;
+  T* outp = reinterpret_cast<T*>(a.out) + row * a.out_stride + a.out_col + ch0;
+  for (int c = lane; c < N; c += 32) {
+    const float g = to_float<T>(gp[c]);
+    const float gate = RULE == 1 ? sigmoidf(g) : g * sigmoidf(g);
+    outp[c] = from_float<T>(o[c] * rstd * a.norm_w[ch0 + c] * gate * a.out_scale);
+  }
+}
+
+template <typename T, int RULE, int NPT, int CPT, int TC, int MAXT>
+int launch_split(const ScanArgs& a, float* prep, float* o_scratch, int rows, cudaStream_t stream) {
+  int KL = 1;
+  while (KL * NPT < a.N) KL <<= 1;
+  const int cons = (((a.N + CPT - 1) / CPT * KL + 31) / 32) * 32;
+  if (cons > MAXT) return -2;
+  const size_t smem = (size_t)2 * (5 * TC * KL * (NPT + 4) + TC * a.N) * sizeof(float);
+  if (smem > 220 * 1024) return -2;
+  cudaError_t e = launch_pdl(recurrence_prepare_kernel<T, RULE>, dim3(rows, a.H), dim3(a.N <= 32 ? 32 : 64),
+                             (size_t)(a.R + 1) * sizeof(float), stream, a, prep);
+  if (e != cudaSuccess) return (int)e;
+  auto kern = recurrence_scan_kernel<T, RULE, NPT, CPT, TC, MAXT>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  e = launch_pdl(kern, dim3(a.n_seqs * a.H), dim3(cons), smem, stream, a, (const float*)prep, o_scratch, KL);
+  if (e != cudaSuccess) return (int)e;
+  const long long warps = (long long)rows * a.H;
+  return (int)launch_pdl(recurrence_finish_kernel<T, RULE>, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, stream, a,
+                         (const float*)o_scratch, rows);
+}
+
+template <typename T, int RULE>
+int pick_split(const ScanArgs& a, float* prep, float* o_scratch, int rows, cudaStream_t stream) {
+  if (a.N <= 64) return launch_split<T, RULE, 16, 2, 32, 128>(a, prep, o_scratch, rows, stream);
+  if (a.N <= 128) return launch_split<T, RULE, 32, 2, 16, 256>(a, prep, o_scratch, rows, stream);
+  return -2;
 }
 
 }  // namespace
@@ -421,8 +623,8 @@ KRK_API int krk_linear_recurrence(int rule, const void* r, int r_stride, const v
                                   const float* rate_bias, const float* bonus, const float* norm_w, float* state,
                                   const void* last_rows, int last_stride, int C, float* last_state, void* out,
                                   int out_stride, int out_col, float out_scale, float eps, float decay_scale, int H, int N,
-                                  int R, int n_seqs, const int* cu_q, const int* seq_qlen, const int* seq_slot, int dtype,
-                                  cudaStream_t stream) {
+                                  int R, int n_seqs, const int* cu_q, const int* seq_qlen, const int* seq_slot, int rows,
+                                  float* prep, float* o_scratch, int dtype, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   ScanArgs a;
   a.r = r; a.k = k; a.v = v; a.g = g; a.rate = rate; a.lora = lora;
@@ -442,6 +644,15 @@ KRK_API int krk_linear_recurrence(int rule, const void* r, int r_stride, const v
   if (rule != 0 && rule != 1) return -2;
   if (rule == 1 && (!rate || !rate_bias)) return -2;
   if (rule == 0 && !bonus) return -2;
+  if (prep && o_scratch && N % 4 == 0 && rows > 0) {
+    // steps of many tokens: prepare, scan, finish (scratch of rows * H * 6 * N and rows * H * N floats)
+    int rc;
+    if (dtype == KRK_DTYPE_F32)
+      rc = rule == 1 ? pick_split<float, 1>(a, prep, o_scratch, rows, stream) : pick_split<float, 0>(a, prep, o_scratch, rows, stream);
+    else
+      rc = rule == 1 ? pick_split<bf16, 1>(a, prep, o_scratch, rows, stream) : pick_split<bf16, 0>(a, prep, o_scratch, rows, stream);
+    if (rc != -2) return rc;
+  }
   if (dtype == KRK_DTYPE_F32)
     return rule == 1 ? pick_recurrence<float, 1>(a, stream) : pick_recurrence<float, 0>(a, stream);
   return rule == 1 ? pick_recurrence<bf16, 1>(a, stream) : pick_recurrence<bf16, 0>(a, stream);

@@ -291,6 +291,13 @@ def test_scans_do_not_depend_on_the_cut_to_the_bit():
     whole = run_part(part, rt, h, [90], torch.float32)
     for pieces in ([1] * 90, [16, 16, 1, 15, 42], [89, 1]):
         assert torch.equal(run_part(part, rt, h, pieces, torch.float32), whole), pieces
+    # the optional three-kernel form of many-token steps forms the same sums in the same order
+    rt.ops.split_recurrence = True
+    try:
+        for pieces in ([90], [40, 33, 17]):
+            assert torch.equal(run_part(part, rt, h, pieces, torch.float32), whole), ("split", pieces)
+    finally:
+        rt.ops.split_recurrence = False
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
