@@ -42,7 +42,7 @@ CONFIGS = {
     "tb": {"architecture": "Taredra", "vocab": 301, "width": 96, "embedding": {"scale": 5.0}, "norm": {"eps": 1e-6},
            "layers": [
                {"type": "parallel", "mlp": {"kind": "dense", "ff": 136},
-                "mixer": {"left": _left(6, 1, 32, 32, 70, 16, 20000.0, 0.18), "right": {"heads": 2, "dim": 32},
+                "mixer": {"left": _left(6, 1, 32, 32, 70, 16, 15000.0, 0.18), "right": {"heads": 2, "dim": 32},
                           "left_scale": 0.9, "right_scale": 1.1}},
                {"type": "wkv", "mixer": {"heads": 3, "dim": 32}, "mlp": None},
                {"type": "wkv", "mixer": {"heads": 1, "dim": 64}, "mlp": {"kind": "dense", "ff": 40}},
