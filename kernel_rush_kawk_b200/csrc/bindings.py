@@ -588,7 +588,7 @@ class Kernels:
             _ptr(last_state), optr, ostride, out_col, float(out_scale), float(eps), float(decay_scale), heads, dim,
             lora.shape[1], batch.n_seqs, batch.cu_q.data_ptr(), batch.seq_qlen.data_ptr(), batch.seq_slot.data_ptr(),
             rows, _ptr(prep), _ptr(o_raw), _code(r.dtype), self._stream())
-        self._ok(rc, f"{kind} recurrence (heads of up to 128 channels)")
+        self._ok(rc, f"{kind} recurrence (heads of up to 256 channels)")
 
     # -- token selection ------------------------------------------------------------
     def select_tokens(self, logits, temperature, seed, requests, step, feed=None, out=None):

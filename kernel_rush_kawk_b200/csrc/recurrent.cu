@@ -412,7 +412,9 @@ template <typename T, int RULE>
 int pick_recurrence(const ScanArgs& a, cudaStream_t stream) {
   if (a.N <= 64) return launch_recurrence<T, RULE, 16, 2, 32, 256, 384>(a, stream);
   if (a.N <= 128) return launch_recurrence<T, RULE, 32, 2, 16, 128, 384>(a, stream);
-  return -2;  // a head's state no longer fits the registers of one block
+  // larger heads: four columns a thread; the state then spills from the registers, which is slow and right
+  if (a.N <= 256) return launch_recurrence<T, RULE, 32, 4, 8, 128, 640>(a, stream);
+  return -2;  // a head's state no longer fits one block
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -237,7 +237,7 @@ def test_one_key_at_the_windows_edge(dtype, window, spike_at, T):
 
 
 STATE_SHAPES = [(64, 3, 16, 8), (48, 1, 48, 16), (96, 2, 32, 5), (64, 1, 64, 16), (40, 5, 8, 3), (64, 1, 128, 4),
-                (40, 2, 20, 3), (30, 2, 5, 2), (72, 1, 100, 40)]
+                (40, 2, 20, 3), (30, 2, 5, 2), (72, 1, 100, 40), (48, 1, 160, 6), (32, 1, 256, 4)]
 
 
 def state_weights(kind, C, H, N, R, seed):
