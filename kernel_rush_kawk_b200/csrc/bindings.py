@@ -60,7 +60,8 @@ _MIX_SIGNATURES = {
     "krk_sink_attention": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P,
                            c_int, _P, _P, c_int, c_float, c_int, c_int, _P],
     "krk_sink_attention_single": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
-                                  c_int, _P, _P, c_int, c_float, c_int, c_int, _P, c_int, _P],
+                                  c_int, _P, _P, c_int, c_float, c_int, c_int, _P, c_int, c_int, c_int, _P, c_int, c_int, c_float,
+                                  c_int, _P],
     "krk_token_shift": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P],
     "krk_linear_recurrence": [c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, _P, _P, _P, _P,
                               _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int,
@@ -134,6 +135,11 @@ class Kernels:
         # steps of many tokens: prepare / scan / finish kernels instead of the fused one. Bit-equal to it and, on one
         # prompt, no faster (the scan itself bounds both), so it is off; it needs rows * channels * 28 bytes of scratch
         self.split_recurrence = False
+        # single-token steps: rotation, value norm and cache write inside the attention kernel (one launch fewer a
+        # layer). Right, and slower (8 sequences of the 1.5k-wide preset: 0.608 against 0.563 ms a step; one sequence
+        # 0.510 against 0.497): every block of an item repeats the prologue on its critical path, where the kernel of
+        # its own runs under the product before it. Off.
+        self.fuse_single_token_attention = os.environ.get("KRK_FUSE_SINGLE_ATTENTION") is not None
         self.launches = 0
 
     def _attn_lib(self, head_dim: int) -> ctypes.CDLL:
@@ -512,7 +518,19 @@ class Kernels:
             batch.seq_slot.data_ptr(), cache.table.data_ptr(), cache.width, cache.k.data_ptr(), cache.v.data_ptr(),
             proj.shape[0], _code(proj.dtype), self._stream()), "rotation + value norm + cache write")
 
-    def sink_attention(self, proj, q_col, heads, dim, vdim, sink, scale, window, batch, cache, out, out_col, out_scale):
+    def sink_attention_step(self, proj, q_col, k_col, v_col, heads, kv_heads, dim, vdim, inv_freq, rot_dims, value_eps, sink,
+                            scale, window, batch, cache, out, out_col, out_scale) -> bool:
+        """Rotation, value norm, cache write and attention of a single-token step as one launch (plus the merge of
+        the blocks' shares). False if the step or the sizes are not of that kind: nothing was done then."""
+        if not self.fuse_single_token_attention:
+            return False
+        if not (batch.is_decode and proj.shape[0] == batch.n_seqs) or heads // kv_heads > 8 or vdim > 128:
+            return False
+        return self.sink_attention(proj, q_col, heads, dim, vdim, sink, scale, window, batch, cache, out, out_col, out_scale,
+                                   fuse=(k_col, v_col, inv_freq, rot_dims, value_eps))
+
+    def sink_attention(self, proj, q_col, heads, dim, vdim, sink, scale, window, batch, cache, out, out_col, out_scale,
+                       fuse=None):
         ptr, stride = self._rows_view(proj)
         optr, ostride = self._rows_view(out)
         if batch.is_decode and proj.shape[0] == batch.n_seqs:
@@ -531,10 +549,16 @@ class Kernels:
                 optr, ostride, out_col, float(out_scale), ptr, stride, q_col, heads, cache.kv_heads, dim, vdim,
                 _ptr(sink), batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), cache.table.data_ptr(), cache.width,
                 cache.k.data_ptr(), cache.v.data_ptr(), batch.n_seqs, float(scale), int(window or 0), splits,
-                _ptr(scratch), _code(proj.dtype), self._stream())
+                _ptr(scratch), *((1, fuse[0], fuse[1], fuse[2].data_ptr(), fuse[3], int(fuse[4] is not None),
+                                  float(fuse[4] or 0.0)) if fuse else (0, 0, 0, None, 0, 0, 0.0)),
+                _code(proj.dtype), self._stream())
             if rc != -2:  # -2: heads too large for it; the general kernel takes them
                 self._ok(rc, "single-token windowed attention with a sink")
-                return
+                return True
+            if fuse:
+                return False
+        elif fuse:
+            return False
         if (proj.dtype == torch.bfloat16 and dim == vdim and dim % 16 == 0 and dim <= 256 and dim in self.attn
                 and not batch.is_decode and hasattr(self.attn[dim], "krk_sink_window_prefill")):
             # many tokens per sequence in bfloat16: the tensor-core walk over whole pages (compiled per head size)

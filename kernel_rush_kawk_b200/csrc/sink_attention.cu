@@ -219,17 +219,23 @@ template <> __device__ __forceinline__ void load4<bf16>(const bf16* p, float* f,
 }
 
 // V4: value heads of a multiple of 4 elements up to 128, lane l holding elements 4l .. 4l + 3 of a row
-template <typename T, bool V4>
+template <typename T, bool V4, bool FUSE>
 __global__ void __launch_bounds__(SINGLE_WARPS * 32)
 sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, float out_scale,
                              const T* __restrict__ proj, int stride, int q_col, int HQ, int HKV, int D, int DV,
                              const float* __restrict__ sink, const int* __restrict__ seq_slot,
                              const int* __restrict__ seq_start, const int* __restrict__ table, int width,
                              const T* __restrict__ k_cache, const T* __restrict__ v_cache, float scale, int window,
-                             int g0, int GN, int SPL, float* __restrict__ scratch) {
+                             int g0, int GN, int SPL, float* __restrict__ scratch, int k_col, int v_col,
+                             const float* __restrict__ inv_freq, int rot, int value_norm, float eps, T* k_cache_w,
+                             T* v_cache_w) {
   extern __shared__ __align__(16) float sm1[];
   float* q_s = sm1;                       // [GN][D]
   float* part = q_s + GN * D;             // [warps][GN][DV + 2]
+  // fused form: the new token's rotated key and normalised value, as the cache stores them
+  T* kn = reinterpret_cast<T*>(sm1 + ((GN * D + SINGLE_WARPS * GN * (DV + 2) + 3) & ~3));
+  T* vn = kn + ((D + 7) & ~7);
+  __shared__ float rstd_s;
   grid_launch_dependents();
   grid_dependency_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -243,6 +249,52 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
   const T* q = proj + (size_t)seq * stride + q_col + (size_t)head0 * D;
   for (int i = threadIdx.x; i < GN * D; i += blockDim.x) q_s[i] = to_float<T>(q[i]);
   __syncthreads();
+  if (FUSE) {
+    // what krk_rotate_norm_write does for this (sequence, kv head), here: the queries are rotated in shared memory,
+    // the new key and value are made once per block and, by the item's first block, written to their page
+    const float p = (float)pos;
+    const int half = rot >> 1;
+    for (int i = threadIdx.x; i < GN * half; i += blockDim.x) {
+      const int g = i / half, j = i % half;
+      float sn, cs;
+      angle_sincos(p, inv_freq[j], inv_freq[half + j], &sn, &cs);
+      const float u = q_s[g * D + j], v = q_s[g * D + j + half];
+      q_s[g * D + j] = round_to<T>(u * cs - v * sn);
+      q_s[g * D + j + half] = round_to<T>(v * cs + u * sn);
+    }
+    const T* kr = proj + (size_t)seq * stride + k_col + (size_t)kh * D;
+    const T* vr = proj + (size_t)seq * stride + v_col + (size_t)kh * DV;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      float sn, cs;
+      angle_sincos(p, inv_freq[j], inv_freq[half + j], &sn, &cs);
+      const float u = to_float<T>(kr[j]), v = to_float<T>(kr[j + half]);
+      kn[j] = from_float<T>(u * cs - v * sn);
+      kn[j + half] = from_float<T>(v * cs + u * sn);
+    }
+    for (int j = rot + threadIdx.x; j < D; j += blockDim.x) kn[j] = kr[j];
+    if (warp == 0) {
+      float rstd = 1.f;
+      if (value_norm) {
+        float sq = 0.f;
+        for (int j = lane; j < DV; j += 32) {
+          const float f = to_float<T>(vr[j]);
+          sq += f * f;
+        }
+        rstd = rsqrtf(warp_sum(sq) / (float)DV + eps);
+      }
+      if (lane == 0) rstd_s = rstd;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < DV; j += blockDim.x) vn[j] = from_float<T>(to_float<T>(vr[j]) * rstd_s);
+    __syncthreads();
+    if (split == 0) {
+      const int page = page_of(table, width, slot, pos);
+      T* kd = k_cache_w + (((size_t)page * HKV + kh) * KRK_PAGE + (pos % KRK_PAGE)) * D;
+      T* vd = v_cache_w + (((size_t)page * HKV + kh) * KRK_PAGE + (pos % KRK_PAGE)) * DV;
+      for (int j = threadIdx.x; j < D; j += blockDim.x) kd[j] = kn[j];
+      for (int j = threadIdx.x; j < DV; j += blockDim.x) vd[j] = vn[j];
+    }
+  }
 
   float m[GROUP_MAX], l[GROUP_MAX], acc[GROUP_MAX][MAX_V_PER_LANE / 2];
 #pragma unroll
@@ -262,7 +314,8 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
     int my_page = 0;
     if (key <= pos) {
       my_page = page_of(table, width, slot, key);
-      const T* kp = k_cache + (((size_t)my_page * HKV + kh) * KRK_PAGE + (key % KRK_PAGE)) * D;
+      const T* kp = (FUSE && key == pos) ? kn  // the new token's key is not in its page for every block yet
+                                         : k_cache + (((size_t)my_page * HKV + kh) * KRK_PAGE + (key % KRK_PAGE)) * D;
       if (vec) {
         // 64 elements of the key row are requested at once (a row is a lane's own, nothing shares its
         // latency), then multiplied with every head's query
@@ -324,7 +377,7 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
         const int j = j0 + jj;
         const int kj = base + j;
         const int page = __shfl_sync(0xffffffffu, my_page, j & 31);  // lane j looked its key's page up already
-        const T* vp = v_cache + (((size_t)page * HKV + kh) * KRK_PAGE + (kj % KRK_PAGE)) * DV;
+        const T* vp = (FUSE && kj == pos) ? vn : v_cache + (((size_t)page * HKV + kh) * KRK_PAGE + (kj % KRK_PAGE)) * DV;
         if (V4) {  // four neighbouring elements per lane, one load
           load4<T>(vp + 4 * lane, vf[jj], j < n && 4 * lane < DV);
         } else {
@@ -477,38 +530,54 @@ KRK_API int krk_sink_attention(void* out, int out_stride, int out_col, float out
 
 // One token per sequence: rows are the sequences, in order. Value heads of up to 128 elements; others take
 // krk_sink_attention. splits > 1: that many blocks share an item's keys and a merge kernel follows; scratch then
-// holds n_seqs * HQ * splits * (DV + 2) floats.
+// holds n_seqs * HQ * splits * (DV + 2) floats. fuse: the kernel also does what krk_rotate_norm_write does for the
+// step's rows (queries rotated on the way in, the new key and value made in shared memory and written to their page
+// by the item's first block), so that a single-token step needs no launch of that kernel.
 KRK_API int krk_sink_attention_single(void* out, int out_stride, int out_col, float out_scale, const void* proj, int stride,
                                       int q_col, int HQ, int HKV, int D, int DV, const float* sink, const int* seq_slot,
                                       const int* seq_start, const int* table, int width, const void* k_cache,
                                       const void* v_cache, int n_seqs, float scale, int window, int splits,
-                                      float* scratch, int dtype, cudaStream_t stream) {
+                                      float* scratch, int fuse, int k_col, int v_col, const float* inv_freq, int rot,
+                                      int value_norm, float eps, int dtype, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (DV > 32 * (MAX_V_PER_LANE / 2) || D > 1024) return -2;
   const int G = HQ / HKV;
   const int SPL = (splits > 1 && scratch) ? splits : 1;
+  if (fuse && G > GROUP_MAX) return -2;  // the new key and value are made by one launch per item
+  if (fuse && (rot < 0 || rot > D || (rot & 1))) return -2;
   for (int g0 = 0; g0 < G; g0 += GROUP_MAX) {
     const int GN = min(GROUP_MAX, G - g0);
-    const size_t smem = ((size_t)GN * D + (size_t)SINGLE_WARPS * GN * (DV + 2)) * sizeof(float);
+    const size_t esz = dtype == KRK_DTYPE_F32 ? 4 : 2;
+    const size_t smem = ((size_t)GN * D + (size_t)SINGLE_WARPS * GN * (DV + 2) + 4) * sizeof(float) +
+                        (((size_t)D + 7) / 8 * 8 + DV + 8) * esz;
     if (smem > 96 * 1024) return -2;
     cudaError_t e;
     const bool v4 = (DV & 3) == 0;  // rows of the value cache then start on 8-byte (16 for float) boundaries
     if (smem > 48 * 1024) {
-      cudaFuncSetAttribute(sink_attention_single_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-      cudaFuncSetAttribute(sink_attention_single_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-      cudaFuncSetAttribute(sink_attention_single_kernel<bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-      cudaFuncSetAttribute(sink_attention_single_kernel<bf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      const int big = 100 * 1024;
+      cudaFuncSetAttribute(sink_attention_single_kernel<float, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+      cudaFuncSetAttribute(sink_attention_single_kernel<float, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+      cudaFuncSetAttribute(sink_attention_single_kernel<bf16, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+      cudaFuncSetAttribute(sink_attention_single_kernel<bf16, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+      cudaFuncSetAttribute(sink_attention_single_kernel<float, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+      cudaFuncSetAttribute(sink_attention_single_kernel<float, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+      cudaFuncSetAttribute(sink_attention_single_kernel<bf16, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+      cudaFuncSetAttribute(sink_attention_single_kernel<bf16, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
     }
     if (dtype == KRK_DTYPE_F32)
-      e = launch_pdl(v4 ? sink_attention_single_kernel<float, true> : sink_attention_single_kernel<float, false>,
+      e = launch_pdl(fuse ? (v4 ? sink_attention_single_kernel<float, true, true> : sink_attention_single_kernel<float, false, true>)
+                          : (v4 ? sink_attention_single_kernel<float, true, false> : sink_attention_single_kernel<float, false, false>),
                      dim3(n_seqs * HKV * SPL), dim3(SINGLE_WARPS * 32), smem, stream,
                      (float*)out, out_stride, out_col, out_scale, (const float*)proj, stride, q_col, HQ, HKV, D, DV, sink,
-                     seq_slot, seq_start, table, width, (const float*)k_cache, (const float*)v_cache, scale, window, g0, GN, SPL, scratch);
+                     seq_slot, seq_start, table, width, (const float*)k_cache, (const float*)v_cache, scale, window, g0, GN, SPL, scratch, k_col, v_col,
+                     inv_freq, rot, value_norm, eps, (float*)k_cache, (float*)v_cache);
     else
-      e = launch_pdl(v4 ? sink_attention_single_kernel<bf16, true> : sink_attention_single_kernel<bf16, false>,
+      e = launch_pdl(fuse ? (v4 ? sink_attention_single_kernel<bf16, true, true> : sink_attention_single_kernel<bf16, false, true>)
+                          : (v4 ? sink_attention_single_kernel<bf16, true, false> : sink_attention_single_kernel<bf16, false, false>),
                      dim3(n_seqs * HKV * SPL), dim3(SINGLE_WARPS * 32), smem, stream,
                      (bf16*)out, out_stride, out_col, out_scale, (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink,
-                     seq_slot, seq_start, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale, window, g0, GN, SPL, scratch);
+                     seq_slot, seq_start, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale, window, g0, GN, SPL, scratch, k_col, v_col,
+                     inv_freq, rot, value_norm, eps, (bf16*)k_cache, (bf16*)v_cache);
     if (e != cudaSuccess) return (int)e;
   }
   if (SPL > 1) {

@@ -81,6 +81,11 @@ class SinkWindowAttention(Branch):
         ops = ctx.ops
         k_col = self.heads * self.dim
         v_col = k_col + self.kv_heads * self.dim
+        value_eps = self.eps if self.value_norm else None
+        if ctx.batch.is_decode and ops.sink_attention_step(proj, 0, k_col, v_col, self.heads, self.kv_heads, self.dim,
+                                                           self.vdim, self.inv_freq, self.rot_dims, value_eps, self.sink,
+                                                           self.scale, self.window, ctx.batch, cache, out, col0, scale):
+            return  # a single-token step: one kernel rotates, writes the cache and attends
         ops.rotate_norm_write(proj, 0, k_col, v_col, self.heads, self.kv_heads, self.dim, self.vdim, self.inv_freq,
                               self.rot_dims, self.eps if self.value_norm else None, ctx.batch, cache)
         ops.sink_attention(proj, 0, self.heads, self.dim, self.vdim, self.sink, self.scale, self.window, ctx.batch, cache,

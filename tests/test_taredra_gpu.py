@@ -454,6 +454,32 @@ def test_long_decoding_past_every_window_and_ring(folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_single_token_steps_with_the_fused_attention_option(folders, dtype):
+    """The option that rotates, normalises and writes the new key and value inside the single-token attention
+    kernel: the same logits as the plain implementation, through captured steps of an unequal batch."""
+    from kernel_rush_kawk_b200 import StepEntry
+
+    name = "tb"
+    engine = engine_for(folders[name], dtype)
+    engine.ops.fuse_single_token_attention = True
+    try:
+        seqs = prompts(name, [90, 150], seed=18)
+        slots = [engine.cache.alloc() for _ in seqs]
+        cut = [10, 75]
+        got = [[engine.step([StepEntry(sl, s[:c], list(range(c)))]).clone()] for sl, s, c in zip(slots, seqs, cut)]
+        fed = list(cut)
+        while any(f < len(s) for f, s in zip(fed, seqs)):
+            live = [i for i in range(2) if fed[i] < len(seqs[i])]
+            out = engine.step([StepEntry(slots[i], [seqs[i][fed[i]]], [0]) for i in live])
+            for r, i in enumerate(live):
+                got[i].append(out[r:r + 1].clone()); fed[i] += 1
+        for i, seq in enumerate(seqs):
+            assert_logits(torch.cat(got[i]), plain_logits(folders[name], seq), dtype, f"fused option, request {i}")
+    finally:
+        engine.ops.fuse_single_token_attention = False
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_engine(folders, dtype):
     """Engine.generate (the scheduler, the captured single-token step, the selection kernel) against
     the plain implementation's argmax, token by token, ties within the arithmetic's noise allowed."""

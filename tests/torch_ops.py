@@ -243,6 +243,13 @@ class _WideOps:
             row0 += n
         out[:, out_col:out_col + heads * vdim] = (res * out_scale).to(out.dtype).view(rows, heads * vdim)
 
+    def sink_attention_step(self, proj, q_col, k_col, v_col, heads, kv_heads, dim, vdim, inv_freq, rot_dims, value_eps, sink,
+                            scale, window, batch, cache, out, out_col, out_scale):
+        self.rotate_norm_write(proj, q_col, k_col, v_col, heads, kv_heads, dim, vdim, inv_freq, rot_dims, value_eps, batch,
+                               cache)
+        self.sink_attention(proj, q_col, heads, dim, vdim, sink, scale, window, batch, cache, out, out_col, out_scale)
+        return True
+
     def token_shift(self, h, last_state, mu, batch):
         hf = h.float()
         prev = torch.empty_like(hf)
