@@ -11,6 +11,8 @@ different places).
                     | parallel(left 2/2 heads dim 24 vdim 8 window 37 rot 24; right 1 x 48, rank 12; ff 72)
   tb     96   301   parallel(left 6/1 heads dim 32 vdim 32 window 70 rot 16; right 2 x 32; ff 136) | wkv(3 x 32, no ff)
                     | wkv(1 x 64, ff 40) | parallel(left 3/3 heads dim 8 vdim 40 window 5 rot 2; right 5 x 8; ff 96)
+  tc     50    97   parallel(left 3/3 heads dim 6 vdim 5 window 3 rot 4; right 1 x 7, rank 3; ff 33) | wkv(3 x 9, rank 5, no ff)
+                    (nothing a multiple of 4 or 8: every kernel's plain path, the products' fallbacks, padded columns)
 """
 
 from __future__ import annotations
@@ -50,8 +52,15 @@ CONFIGS = {
                 "mixer": {"left": _left(3, 3, 8, 40, 5, 2, 10.0, 0.5), "right": {"heads": 5, "dim": 8},
                           "left_scale": 0.5, "right_scale": 1.5}},
            ]},
+    "tc": {"architecture": "Taredra", "vocab": 97, "width": 50, "embedding": {"scale": 2}, "norm": {"eps": 1e-5},
+           "layers": [
+               {"type": "parallel", "mlp": {"kind": "dense", "ff": 33},
+                "mixer": {"left": _left(3, 3, 6, 5, 3, 4, 7.0, 0.4), "right": {"heads": 1, "dim": 7, "rank": 3},
+                          "left_scale": 1, "right_scale": 2}},
+               {"type": "wkv", "mixer": {"heads": 3, "dim": 9, "rank": 5}, "mlp": None},
+           ]},
 }
-SEEDS = {"ta": 5, "tb": 6}
+SEEDS = {"ta": 5, "tb": 6, "tc": 7}
 
 
 def config(name: str):
