@@ -62,7 +62,8 @@ class FreeList:
 class PageLedger:
     """Pages of one storage group: a pool and, per slot, the pages it holds in
     logical order. ``ring`` is None for a group that keeps every position, or the
-    number of logical pages a slot cycles through for a group that keeps a window."""
+    number of logical pages a slot holds at most for a group that keeps a window (the
+    pages of positions that are kept for good come first and count among them)."""
 
     def __init__(self, n_pages: int, n_slots: int, width: int, page_size: int, ring: int | None):
         self.pool = FreeList(n_pages, "cache page")

@@ -39,11 +39,15 @@ class KVView:
     k: torch.Tensor  # [pages, kv_heads, PAGE, head_dim]
     v: torch.Tensor  # [pages, kv_heads, PAGE, v_dim]; v_dim is head_dim unless the need says otherwise
     table: torch.Tensor  # int32 [slots, width] on the device
-    width: int  # logical pages per slot; position p is in table[slot, (p // PAGE) % width]
+    width: int  # logical pages per slot; position p is in table[slot, (p // PAGE) % width] (but see keep_pages)
     window: int | None
     kv_heads: int
     head_dim: int
     v_dim: int = 0
+    #: the first ``keep_pages`` logical pages hold the sequence's first positions for good; later positions
+    #: cycle through the others: page index b = p // PAGE sits in entry b if b < keep_pages, else in entry
+    #: keep_pages + (b - keep_pages) % (width - keep_pages)
+    keep_pages: int = 0
 
     def __post_init__(self):
         self.v_dim = self.v_dim or self.head_dim
@@ -56,20 +60,23 @@ class StateView:
 
 class _KVGroup:
     def __init__(self, need: KVNeed, runs: list[int], n_pages: int, n_slots: int, width: int, ring: int | None,
-                 device, dtype):
+                 device, dtype, keep_pages: int = 0):
         self.need = need
         self.runs = runs
         self.width = ring if ring is not None else width
+        self.keep_pages = keep_pages if ring is not None else 0
         self.ledger = PageLedger(n_pages, n_slots, self.width, PAGE, ring)
         shape = (len(runs), n_pages, need.kv_heads, PAGE, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape[:-1] + (need.v_dim or need.head_dim,), dtype=dtype, device=device)
+        # a group without values of its own hands its keys out as values (one row per position serves as both)
+        self.v = self.k if not need.values else torch.zeros(shape[:-1] + (need.v_dim or need.head_dim,), dtype=dtype,
+                                                           device=device)
         self.table_host = np.zeros((n_slots, self.width), dtype=np.int32)
         self.table = torch.zeros((n_slots, self.width), dtype=torch.int32, device=device)
         self.dirty: set[int] = set()
 
     def bytes(self) -> int:
-        return (self.k.numel() + self.v.numel()) * self.k.element_size()
+        return (self.k.numel() + (self.v.numel() if self.need.values else 0)) * self.k.element_size()
 
 
 class _StateGroup:
@@ -121,10 +128,13 @@ class SequenceCache:
             if isinstance(need, KVNeed):
                 ring = None
                 pages = self.n_pages
+                keep_pages = 0
                 if need.window is not None:
-                    ring = min(self.width, -(-(need.window + self.step_tokens - 1) // PAGE) + 1)
+                    keep_pages = -(-max(0, int(need.keep_first)) // PAGE)
+                    ring = min(self.width, keep_pages + -(-(need.window + self.step_tokens - 1) // PAGE) + 1)
+                    keep_pages = min(keep_pages, ring - 1)  # a context this short never reaches the ring's turn
                     pages = min(self.n_pages, self.max_slots * ring)
-                group = _KVGroup(need, runs, pages, self.max_slots, self.width, ring, self.device, dtype)
+                group = _KVGroup(need, runs, pages, self.max_slots, self.width, ring, self.device, dtype, keep_pages)
                 self._kv_groups.append(group)
             else:
                 group = _StateGroup(need, runs, self.max_slots, self.device, dtype)
@@ -214,7 +224,8 @@ class SequenceCache:
     def _view_of(group, line):
         if isinstance(group, _KVGroup):
             return KVView(group.k[line], group.v[line], group.table, group.width, group.need.window,
-                          group.need.kv_heads, group.need.head_dim, group.need.v_dim or group.need.head_dim)
+                          group.need.kv_heads, group.need.head_dim, group.need.v_dim or group.need.head_dim,
+                          group.keep_pages)
         return StateView(group.state[line])
 
     # -- accounting ---------------------------------------------------------

@@ -65,8 +65,9 @@ class PartTree:
                 built += [ffn_norm, ffn]
             if self.position is not None and hasattr(mixer.part, "set_position"):
                 mixer.part.set_position(self.position.part)
+            extra = () if spec.block_params is None else (dict(spec.block_params),)
             block = parts_base.block_class(spec.block)(mixer_norm.part, mixer.part, ffn_norm and ffn_norm.part,
-                                                       ffn and ffn.part)
+                                                       ffn and ffn.part, *extra)
             self.layers.append((block, built))
         for i, entry in enumerate(plan.schedule):
             mixer = self.layers[entry.layer][0].mixer
@@ -154,11 +155,14 @@ class Model:
         if self.position is not None:
             x = self.position.on_embeddings(ctx, x)
         stream = Stream(x)
+        ctx.shared = {}  # what a layer leaves for later layers of the same step (values that they blend in, say)
         for run, entry in enumerate(self.plan.schedule):
             stream = self.blocks[entry.layer].forward(ctx, stream, ctx.cache_view(run))
         if want_rows is not None and not getattr(ctx.batch, "want_all", False):  # all rows in order: nothing to gather
             stream.x = ops.gather_rows(stream.x, want_rows)
             if stream.branch is not None:
                 stream.branch = ops.gather_rows(stream.branch, want_rows)
+            if stream.branch2 is not None:
+                stream.branch2 = ops.gather_rows(stream.branch2, want_rows)
         h = self.final_norm.forward(ctx, stream)
         return self.head.forward(ctx, h)

@@ -132,6 +132,7 @@ class StepContext:
         self.ops = ops
         self.batch = batch
         self.cache = cache
+        self.shared: dict = {}  # set anew by every run of the model: what a layer leaves for later layers of the step
 
     def cache_view(self, run: int):
         return self.cache.view(run)

@@ -9,11 +9,13 @@ from .norm import Normed, RMSNorm
 from .rope import RotaryTable
 from .attention import GQAttention
 from .mlp import SwiGLU
-from .block import PreNormBlock
+from .block import ParallelResidualBlock, PreNormBlock
 from .embedding import OutputHead, TokenEmbedding
 from .wide import GatedMLP, ScaledEmbedding, WideRMSNorm
 from .branches import Branch, ParallelMixer
 from .sink_attention import SinkWindowAttention
 from .recurrent import DeltaRule, TimeMixWKV
+from .latent_attention import LatentAttention
+from .moe import RoutedExperts
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -47,6 +47,12 @@ class KVNeed:
     window: int | None = None
     #: size of a value head where it differs from the key head's (None: the same)
     v_dim: int | None = None
+    #: a window group also keeps the sequence's first ``keep_first`` positions for good (their pages never
+    #: join the ring)
+    keep_first: int = 0
+    #: False: one row per position serves as key and as value (a latent row that both are made from); no
+    #: value storage is kept and a view's ``v`` is its ``k``
+    values: bool = True
 
 
 @dataclass(frozen=True)
@@ -150,13 +156,19 @@ class Stream:
     """The residual stream between parts: ``x`` [rows, hidden] and a branch output
     that has not been added yet. The next norm adds it (one fused kernel does the
     add, writes the new ``x`` and normalises), which is how the reference fuses the
-    residual add with the following RMSNorm (engine/model.py:300-302)."""
+    residual add with the following RMSNorm (engine/model.py:300-302).
 
-    __slots__ = ("x", "branch")
+    A layer whose mixer and feed-forward read the same x leaves two pending outputs
+    (``branch`` and ``branch2``) and a multiplier for their sum (``scale``):
+    the next norm computes x + scale * (branch + branch2)."""
 
-    def __init__(self, x, branch=None):
+    __slots__ = ("x", "branch", "branch2", "scale")
+
+    def __init__(self, x, branch=None, branch2=None, scale=1.0):
         self.x = x
         self.branch = branch
+        self.branch2 = branch2
+        self.scale = scale
 
 
 # ----------------------------------------------------------------------------

@@ -47,6 +47,12 @@ class LayerSpec:
     mixer: PartSpec
     feed_forward_norm: PartSpec | None = None
     feed_forward: PartSpec | None = None
+    #: constants of the arrangement itself (a multiplier of the layer's output, say); None: it has none
+    block_params: Mapping | None = None
+
+    def __post_init__(self):
+        if self.block_params is not None:
+            object.__setattr__(self, "block_params", _frozen(self.block_params))
 
 
 @dataclass(frozen=True)

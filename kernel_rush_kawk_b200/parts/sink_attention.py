@@ -9,6 +9,15 @@ of 0..p); score = (q . k) * scale with ``scale`` a parameter; with ``sink`` each
 head's softmax has one more term in its denominator, exp(sink_h), which carries
 no value. Key and value heads may differ in size (``dim``, ``vdim``). Scores and
 weights are 32-bit; the weights multiply the values unrounded.
+
+Three more options, each off by default. ``keep_first``: a windowed query also sees
+the sequence's first ``keep_first`` keys, at their true positions (the cache keeps
+their pages out of the window's ring). ``gate``: the heads' outputs are multiplied
+by sigmoid(Wg h) before the output projection, one number per head ("head") or per
+element ("element"); Wg h rides in the stacked input product. ``value_mix``: values
+are blended across layers of one step: the layer marked "first" leaves its values of
+the step's tokens under ``value_mix_key``, a layer marked "blend" caches
+(1 - lambda) v + lambda v_first with its own scalar lambda (tensor "vmix").
 """
 
 from __future__ import annotations
@@ -21,7 +30,8 @@ from .branches import Branch
 
 class SinkWindowAttention(Branch):
     """params: hidden, heads, kv_heads, dim, vdim, scale, window (None or int), rot_dims, rot_base,
-    value_norm (bool), sink (bool), eps."""
+    value_norm (bool), sink (bool), eps, keep_first (int), gate (None, "head" or "element"),
+    value_mix (None, "first" or "blend"), value_mix_key."""
 
     def __init__(self, params):
         super().__init__(params)
@@ -38,6 +48,14 @@ class SinkWindowAttention(Branch):
         self.value_norm = bool(p.get("value_norm", False))
         self.has_sink = bool(p.get("sink", False))
         self.eps = float(p.get("eps", 0.0))
+        self.keep_first = int(p.get("keep_first") or 0) if self.window is not None else 0
+        self.gate = p.get("gate")
+        self.value_mix = p.get("value_mix")
+        self.value_mix_key = str(p.get("value_mix_key", "value_mix"))
+        if self.gate not in (None, "head", "element"):
+            raise ValueError(f"gate must be None, 'head' or 'element', got {self.gate!r}")
+        if self.value_mix not in (None, "first", "blend"):
+            raise ValueError(f"value_mix must be None, 'first' or 'blend', got {self.value_mix!r}")
         if self.heads % self.kv_heads:
             raise ValueError(f"heads ({self.heads}) must be a multiple of kv_heads ({self.kv_heads})")
         if self.rot_dims % 2 or self.rot_dims > self.dim:
@@ -50,18 +68,28 @@ class SinkWindowAttention(Branch):
                  "o": TensorSpec((self.hidden, self.heads * self.vdim))}
         if self.has_sink:
             specs["sink"] = TensorSpec((self.heads,), "vector")
+        if self.gate:
+            specs["g"] = TensorSpec((self.heads * (self.vdim if self.gate == "element" else 1), self.hidden))
+        if self.value_mix:
+            specs["vmix"] = TensorSpec((), "vector")  # the first layer of a blend stores one too and never reads it
         return specs
 
     def cache_need(self):
-        return KVNeed(self.kv_heads, self.dim, self.window, None if self.vdim == self.dim else self.vdim)
+        return KVNeed(self.kv_heads, self.dim, self.window, None if self.vdim == self.dim else self.vdim,
+                      keep_first=self.keep_first)
+
+    @property
+    def _plain(self) -> bool:
+        return not (self.keep_first or self.gate or self.value_mix)
 
     def attention_head_dims(self):
         """Steps of many tokens in bfloat16 run on the tensor cores where key and value heads have one size that
         is a multiple of 16: that kernel is compiled per head size."""
-        return (self.dim,) if self.dim == self.vdim and self.dim % 16 == 0 and self.dim <= 256 else ()
+        return (self.dim,) if self._plain and self.dim == self.vdim and self.dim % 16 == 0 and self.dim <= 256 else ()
 
     def bind(self, tensors, runtime):
-        self.w = {k: tensors[k] for k in ("q", "k", "v", "o")}
+        self.w = {k: tensors[k] for k in ("q", "k", "v", "o") + (("g",) if self.gate else ())}
+        self.lam = float(tensors["vmix"].float().item()) if self.value_mix == "blend" else None
         self.sink = tensors["sink"].float().contiguous() if self.has_sink else None
         # the few rotation frequencies come from the host in 64-bit, so that they depend on no device's pow()
         # and as two floats each (the float32 value, then what float32 leaves of the float64 value)
@@ -72,7 +100,7 @@ class SinkWindowAttention(Branch):
         self.bind_standalone()
 
     def in_weight(self):
-        return torch.cat([self.w["q"], self.w["k"], self.w["v"]], dim=0)
+        return torch.cat([self.w["q"], self.w["k"], self.w["v"]] + ([self.w["g"]] if self.gate else []), dim=0)
 
     def out_weight(self):
         return self.w["o"]
@@ -82,6 +110,22 @@ class SinkWindowAttention(Branch):
         k_col = self.heads * self.dim
         v_col = k_col + self.kv_heads * self.dim
         value_eps = self.eps if self.value_norm else None
+        if not self._plain:
+            blend = None
+            if self.value_mix == "first":
+                ctx.shared[self.value_mix_key] = proj[:, v_col:v_col + self.kv_heads * self.vdim]
+            elif self.value_mix == "blend":
+                first = ctx.shared.get(self.value_mix_key)
+                if first is None or first.shape[1] != self.kv_heads * self.vdim:
+                    raise RuntimeError("a layer that blends values runs after the layer that leaves them, with value "
+                                       "heads of the same number and size")
+                blend = (first, self.lam)
+            ops.rotate_norm_write(proj, 0, k_col, v_col, self.heads, self.kv_heads, self.dim, self.vdim, self.inv_freq,
+                                  self.rot_dims, value_eps, ctx.batch, cache, value_mix=blend)
+            gate = (v_col + self.kv_heads * self.vdim, self.gate) if self.gate else None
+            ops.sink_attention(proj, 0, self.heads, self.dim, self.vdim, self.sink, self.scale, self.window, ctx.batch,
+                               cache, out, col0, scale, keep_first=self.keep_first, gate=gate)
+            return
         if ctx.batch.is_decode and ops.sink_attention_step(proj, 0, k_col, v_col, self.heads, self.kv_heads, self.dim,
                                                            self.vdim, self.inv_freq, self.rot_dims, value_eps, self.sink,
                                                            self.scale, self.window, ctx.batch, cache, out, col0, scale):

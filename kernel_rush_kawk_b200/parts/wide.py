@@ -4,7 +4,10 @@
 * ``WideRMSNorm``: y = x / sqrt(mean(x^2) + eps) * (offset + w) with x, the sum
   x + branch and all arithmetic in float32; only y is rounded to the path's
   dtype. ``offset`` 1 serves weights that are stored around zero, 0 the usual
-  gain. The stream it leaves behind (``x_new``) is float32.
+  gain. The stream it leaves behind (``x_new``) is float32. A stream with two
+  pending outputs and a multiplier is folded as x + scale * (branch + branch2);
+  ``forward_pair`` gives two norms of the same x (two gains, one pass over x) for
+  a layer whose mixer and feed-forward both read it.
 * ``GatedMLP``: down(act(gate h) * (up h)) with the activation as a parameter
   (``gelu_tanh``: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), or ``silu``);
   the activation and the product are computed in float32 and rounded once.
@@ -59,16 +62,36 @@ class WideRMSNorm(Norm):
         self.dtype = runtime.dtype
 
     def forward(self, ctx, stream: Stream) -> Normed:
+        return self._run(ctx, stream, None)[0]
+
+    def forward_pair(self, ctx, stream: Stream, other: "WideRMSNorm"):
+        """This norm and ``other`` of the same x (the pending outputs folded in once): two Normed."""
+        if other.eps != self.eps or other.offset != self.offset or other.size != self.size:
+            raise ValueError("two norms of one x share their size, eps and gain offset")
+        return self._run(ctx, stream, other.gain)
+
+    def _run(self, ctx, stream: Stream, gain2):
         x = stream.x
         if x.dtype != torch.float32:
             raise TypeError("a wide norm follows a float32 residual stream (an embedding or norm of the same family)")
-        x_new = ctx.ops.empty_like(x) if stream.branch is not None else x
-        rows = ctx.ops.rmsnorm_wide(x, stream.branch, self.gain, self.offset, self.eps, x_new, self.dtype)
-        normed = Normed(ctx.ops, x, stream.branch, self.gain, self.eps, x_new)
-        normed.mark_fused(rows)  # computed here and now: a product never folds this norm into its prologue
+        branch, branch2 = stream.branch, stream.branch2
+        if branch is None and branch2 is not None:
+            branch, branch2 = branch2, None
+        x_new = ctx.ops.empty_like(x) if branch is not None else x
+        if branch2 is None and gain2 is None and stream.scale == 1.0:
+            rows = ctx.ops.rmsnorm_wide(x, branch, self.gain, self.offset, self.eps, x_new, self.dtype)
+        else:
+            rows = ctx.ops.rmsnorm_wide(x, branch, self.gain, self.offset, self.eps, x_new, self.dtype, branch2=branch2,
+                                        scale=stream.scale, gain2=gain2)
+        out = []
+        for r, g in zip(rows if gain2 is not None else (rows,), (self.gain, gain2)):
+            normed = Normed(ctx.ops, x, branch, g, self.eps, x_new)
+            normed.mark_fused(r)  # computed here and now: a product never folds this norm into its prologue
+            out.append(normed)
         stream.x = x_new
-        stream.branch = None
-        return normed
+        stream.branch = stream.branch2 = None
+        stream.scale = 1.0
+        return out
 
 
 class GatedMLP(FeedForward):

@@ -161,6 +161,15 @@ class TorchOps:
 # and recurrent state (kernel_rush_kawk_b200/csrc/wide_rows.cu, sink_attention.cu, recurrent.cu)
 # ----------------------------------------------------------------------------
 
+def _entry(cache, pos):
+    """The page-table entry of a position: the first ``keep_pages`` entries hold their positions for good."""
+    b = pos // PAGE
+    keep = getattr(cache, "keep_pages", 0)
+    if not keep:
+        return b % cache.width
+    return torch.where(b < keep, b, keep + (b - keep) % max(cache.width - keep, 1))
+
+
 def _act(z, name):
     if name == "silu":
         return z * torch.sigmoid(z)
@@ -175,18 +184,63 @@ class _WideOps:
     def embed_scaled(self, table, tokens, n_rows, scale):
         return table[tokens.long()].float() * scale
 
-    def rmsnorm_wide(self, x, branch, gain, offset, eps, x_new, out_dtype):
-        s = x if branch is None else x + branch.float()
+    def rmsnorm_wide(self, x, branch, gain, offset, eps, x_new, out_dtype, branch2=None, scale=1.0, gain2=None):
+        s = x
         if branch is not None:
+            b = branch.float() if branch2 is None else branch.float() + branch2.float()
+            s = x + (b if scale == 1.0 else b * scale)
             x_new.copy_(s)
-        return (s * torch.rsqrt((s * s).mean(dim=-1, keepdim=True) + eps) * (offset + gain.float())).to(out_dtype)
+        n = s * torch.rsqrt((s * s).mean(dim=-1, keepdim=True) + eps)
+        first = (n * (offset + gain.float())).to(out_dtype)
+        return first if gain2 is None else (first, (n * (offset + gain2.float())).to(out_dtype))
 
     def gate_up_act(self, h, w_gate_up, intermediate, activation):
         gu = self.linear(h, w_gate_up).float()
         return (_act(gu[:, :intermediate], activation) * gu[:, intermediate:2 * intermediate]).to(self.dtype)
 
+    def gated_act(self, gu, intermediate, activation, row_gate_col=None):
+        g = gu.float()
+        out = _act(g[:, :intermediate], activation) * g[:, intermediate:2 * intermediate]
+        if row_gate_col is not None:
+            out = out * torch.sigmoid(g[:, row_gate_col:row_gate_col + 1])
+        return out.to(gu.dtype)
+
+    def latent_norm_write(self, proj, c_col, rank, gain, eps, batch, cache):
+        c = proj[:, c_col:c_col + rank].float()
+        c = c * torch.rsqrt((c * c).mean(dim=-1, keepdim=True) + eps) * gain.float()
+        pos = batch.row_pos.long()
+        slot = batch.seq_slot.long()[batch.row_seq.long()]
+        page = cache.table.long()[slot, _entry(cache, pos)]
+        cache.k[page, 0, pos % PAGE] = c.to(proj.dtype)
+
+    def head_linear(self, x, w, out=None, out_col=0, out_scale=1.0):
+        heads, n, k = w.shape
+        rows = x.shape[0]
+        y = torch.einsum("rhk,hnk->rhn", x.float().reshape(rows, heads, k), w.float()).reshape(rows, heads * n) * out_scale
+        if out is None:
+            return y.to(x.dtype)
+        out[:, out_col:out_col + heads * n] = y.to(out.dtype)
+        return out
+
+    def moe_route(self, x, w, b, top):
+        z = x.float() @ w.float().t() + b.float()
+        best = torch.topk(z, top, dim=-1)  # ties are not exercised: equal logits do not occur with random weights
+        return best.indices.to(torch.int32), torch.softmax(best.values, dim=-1)
+
+    def moe_experts(self, x, w_gate_up, w_down, experts, weights, intermediate, activation, add=None, batch=None):
+        rows, top = experts.shape
+        out = torch.zeros((rows, w_down.shape[1]), dtype=torch.float32) if add is None else add.float().clone()
+        xf = x.float()
+        for r in range(rows):
+            for j in range(top):
+                e = int(experts[r, j])
+                gu = xf[r] @ w_gate_up[e].float().t()
+                a = (_act(gu[:intermediate], activation) * gu[intermediate:]).to(self.dtype).float()
+                out[r] += weights[r, j] * (a @ w_down[e].float().t())
+        return out.to(self.dtype)
+
     def rotate_norm_write(self, proj, q_col, k_col, v_col, heads, kv_heads, dim, vdim, inv_freq, rot_dims, value_eps,
-                          batch, cache):
+                          batch, cache, value_mix=None):
         rows = proj.shape[0]
         pos = batch.row_pos.long()
         half = rot_dims // 2
@@ -205,14 +259,18 @@ class _WideOps:
         q.copy_(rotate(q).to(proj.dtype))
         k = rotate(proj[:, k_col:k_col + kv_heads * dim].reshape(rows, kv_heads, dim)).to(proj.dtype)
         v = proj[:, v_col:v_col + kv_heads * vdim].reshape(rows, kv_heads, vdim).float()
+        if value_mix is not None:
+            first, lam = value_mix
+            v = (1.0 - lam) * v + lam * first.float().reshape(rows, kv_heads, vdim)
         if value_eps is not None:
             v = v * torch.rsqrt((v * v).mean(dim=-1, keepdim=True) + value_eps)
         slot = batch.seq_slot.long()[batch.row_seq.long()]
-        page = cache.table.long()[slot, (pos // PAGE) % cache.width]
+        page = cache.table.long()[slot, _entry(cache, pos)]
         cache.k[page, :, pos % PAGE] = k
         cache.v[page, :, pos % PAGE] = v.to(proj.dtype)
 
-    def sink_attention(self, proj, q_col, heads, dim, vdim, sink, scale, window, batch, cache, out, out_col, out_scale):
+    def sink_attention(self, proj, q_col, heads, dim, vdim, sink, scale, window, batch, cache, out, out_col, out_scale,
+                       keep_first=0, gate=None, gate_rows=None):
         rows = proj.shape[0]
         G = heads // cache.kv_heads
         q = proj[:, q_col:q_col + heads * dim].reshape(rows, heads, dim).float()
@@ -223,13 +281,15 @@ class _WideOps:
             total = start + n
             lo = 0 if window is None else max(0, start - window + 1)
             positions = torch.arange(lo, total, device=proj.device)
-            pages = table[slot, (positions // PAGE) % cache.width]
+            if window is not None and keep_first:
+                positions = torch.cat([torch.arange(0, min(keep_first, lo), device=proj.device), positions])
+            pages = table[slot, _entry(cache, positions)]
             k = cache.k[pages, :, positions % PAGE].float()
             v = cache.v[pages, :, positions % PAGE].float()
             qpos = torch.arange(start, total, device=proj.device)
             visible = positions[None, :] <= qpos[:, None]
             if window is not None:
-                visible &= positions[None, :] > qpos[:, None] - window
+                visible &= (positions[None, :] > qpos[:, None] - window) | (positions[None, :] < keep_first)
             for h in range(heads):
                 s = (q[row0:row0 + n, h] @ k[:, h // G].t()) * scale
                 s = s.masked_fill(~visible, float("-inf"))
@@ -241,6 +301,11 @@ class _WideOps:
                 p = torch.exp(s - m)
                 res[row0:row0 + n, h] = (p @ v[:, h // G]) / (p.sum(dim=-1, keepdim=True) + extra)
             row0 += n
+        if gate is not None:
+            col, mode = gate
+            src = proj if gate_rows is None else gate_rows
+            width = heads * (vdim if mode == "element" else 1)
+            res = res * torch.sigmoid(src[:, col:col + width].float()).reshape(rows, heads, -1)
         out[:, out_col:out_col + heads * vdim] = (res * out_scale).to(out.dtype).view(rows, heads * vdim)
 
     def sink_attention_step(self, proj, q_col, k_col, v_col, heads, kv_heads, dim, vdim, inv_freq, rot_dims, value_eps, sink,
