@@ -53,15 +53,26 @@ _SIGNATURES = {
 }
 _MIX_SIGNATURES = {
     "krk_embed_scaled": [_P, _P, _P, c_int, c_int, c_int, c_float, _P, c_int, _P],
-    "krk_rmsnorm_wide": [_P, _P, _P, _P, _P, c_float, c_int, c_int, c_float, c_int, _P],
-    "krk_gated_act": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "krk_rmsnorm_wide": [_P, _P, _P, _P, _P, c_float, c_int, c_int, c_float, _P, c_float, _P, _P, c_int, _P],
+    "krk_gated_act": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_rotate_norm_write": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_float, _P, _P,
-                              _P, _P, c_int, _P, _P, c_int, c_int, _P],
+                              _P, _P, c_int, _P, _P, c_int, c_int, _P, c_int, c_float, c_int, _P],
     "krk_sink_attention": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P,
-                           c_int, _P, _P, c_int, c_float, c_int, c_int, _P],
+                           c_int, _P, _P, c_int, c_float, c_int, c_int, c_int, _P, c_int, c_int, c_int, c_int, _P],
     "krk_sink_attention_single": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                                   c_int, _P, _P, c_int, c_float, c_int, c_int, _P, c_int, c_int, c_int, _P, c_int, c_int, c_float,
-                                  c_int, _P],
+                                  c_int, c_int, _P, c_int, c_int, c_int, c_int, _P],
+    "krk_latent_norm_write": [_P, c_int, c_int, c_int, _P, c_float, _P, _P, _P, _P, c_int, c_int, _P, c_int, c_int, _P],
+    "krk_head_linear": [_P, c_int, c_int, c_float, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P],
+}
+_MOE_SIGNATURES = {
+    "krk_moe_route": [_P, _P, _P, _P, c_int, c_int, c_int, _P],
+    "krk_moe_gate_up_pairs": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "krk_moe_down_pairs": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "krk_moe_sort": [_P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "krk_moe_combine": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
+}
+_SCAN_SIGNATURES = {
     "krk_token_shift": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P],
     "krk_linear_recurrence": [c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, _P, _P, _P, _P, _P,
                               _P, _P, c_int, c_int, _P, _P, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int,
@@ -116,7 +127,7 @@ class Kernels:
             raise KernelError("no CUDA device: this library computes with its CUDA kernels only")
         self.device = torch.device(device)
         self.core = _load(build_library("core"), _SIGNATURES)
-        self._mix = None
+        self._mix = self._scan = self._moe = None
         self.attn: dict[int, ctypes.CDLL] = {}
         for d in head_dims:
             self._attn_lib(int(d))
@@ -464,6 +475,20 @@ class Kernels:
             self._mix = _load(build_library("mix"), _MIX_SIGNATURES)
         return self._mix
 
+    @property
+    def scan(self) -> ctypes.CDLL:
+        """The library of the recurrent-state kernels, compiled and loaded at their first call."""
+        if self._scan is None:
+            self._scan = _load(build_library("scan"), _SCAN_SIGNATURES)
+        return self._scan
+
+    @property
+    def moe(self) -> ctypes.CDLL:
+        """The library of the routed-experts kernels, compiled and loaded at their first call."""
+        if self._moe is None:
+            self._moe = _load(build_library("moe"), _MOE_SIGNATURES)
+        return self._moe
+
     @staticmethod
     def _rows_view(t):
         """(pointer, row stride) of a 2-D view whose rows are contiguous."""
@@ -478,23 +503,104 @@ class Kernels:
                                            self._stream()), "scaled embedding gather")
         return out
 
-    def rmsnorm_wide(self, x, branch, gain, offset, eps, x_new, out_dtype):
-        """Rows of a float32 stream, normalised into ``out_dtype``; with a branch, ``x_new`` = x + branch (float32)."""
+    def rmsnorm_wide(self, x, branch, gain, offset, eps, x_new, out_dtype, branch2=None, scale=1.0, gain2=None):
+        """Rows of a float32 stream, normalised into ``out_dtype``; with a branch, ``x_new`` = x + scale * (branch +
+        branch2) (float32). With a second gain, two results of the one pass: (rows, rows2)."""
         if x.dtype != torch.float32 or gain.dtype != torch.float32 or not x.is_contiguous():
             raise KernelError("the wide norm reads a contiguous float32 stream and a float32 gain")
-        if branch is not None and (branch.dtype != out_dtype or not branch.is_contiguous() or branch.shape != x.shape):
-            raise KernelError("the wide norm's branch must have the path's dtype and the stream's shape")
+        for b in (branch, branch2):
+            if b is not None and (b.dtype != out_dtype or not b.is_contiguous() or b.shape != x.shape):
+                raise KernelError("the wide norm's branch must have the path's dtype and the stream's shape")
+        if gain2 is not None and (gain2.dtype != torch.float32 or gain2.shape != gain.shape):
+            raise KernelError("the wide norm's second gain must be float32 and of the first one's size")
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        out2 = torch.empty(x.shape, dtype=out_dtype, device=x.device) if gain2 is not None else None
         self._ok(self.mix.krk_rmsnorm_wide(out.data_ptr(), x_new.data_ptr() if branch is not None else None, x.data_ptr(),
                                            _ptr(branch), gain.data_ptr(), float(offset), x.shape[0], x.shape[1], float(eps),
-                                           _code(out_dtype), self._stream()), "wide rmsnorm")
-        return out
+                                           _ptr(branch2), float(scale), _ptr(gain2), _ptr(out2), _code(out_dtype),
+                                           self._stream()), "wide rmsnorm")
+        return out if gain2 is None else (out, out2)
 
-    def gated_act(self, gu, intermediate, activation):
+    def gated_act(self, gu, intermediate, activation, row_gate_col=None):
+        """act(gu[:, :I]) * gu[:, I:2I], times sigmoid(gu[:, row_gate_col]) per row if that column is given."""
         ptr, stride = self._rows_view(gu)
         out = torch.empty((gu.shape[0], intermediate), dtype=gu.dtype, device=gu.device)
         self._ok(self.mix.krk_gated_act(out.data_ptr(), ptr, stride, gu.shape[0], intermediate, _ACTIVATIONS[activation],
-                                        _code(gu.dtype), self._stream()), "gated activation")
+                                        -1 if row_gate_col is None else int(row_gate_col), _code(gu.dtype),
+                                        self._stream()), "gated activation")
+        return out
+
+    def latent_norm_write(self, proj, c_col, rank, gain, eps, batch, cache):
+        """The rows' ``rank`` columns from ``c_col`` on, RMS-normed with a float32 gain, into the cache (one head)."""
+        ptr, stride = self._rows_view(proj)
+        if cache.k.dtype != proj.dtype or cache.head_dim != rank or cache.kv_heads != 1 or gain.dtype != torch.float32:
+            raise KernelError("the cache does not fit the latent rows it is to receive")
+        self._ok(self.mix.krk_latent_norm_write(ptr, stride, int(c_col), int(rank), gain.data_ptr(), float(eps),
+                                                batch.row_seq.data_ptr(), batch.row_pos.data_ptr(),
+                                                batch.seq_slot.data_ptr(), cache.table.data_ptr(), cache.width,
+                                                int(getattr(cache, "keep_pages", 0)), cache.k.data_ptr(), proj.shape[0],
+                                                _code(proj.dtype), self._stream()), "latent norm + cache write")
+
+    def head_linear(self, x, w, out=None, out_col=0, out_scale=1.0):
+        """out[r, h, :] = out_scale * W_h x[r, h, :]; W [heads, N, K] contiguous, x [rows, heads * K] (rows may be strided)."""
+        heads, N, K = w.shape
+        ptr, stride = self._rows_view(x)
+        if x.shape[1] != heads * K or w.dtype != x.dtype or not w.is_contiguous():
+            raise KernelError("the per-head product reads [rows, heads * K] rows and a contiguous [heads, N, K] weight of one dtype")
+        if out is None:
+            out = torch.empty((x.shape[0], heads * N), dtype=x.dtype, device=x.device)
+        optr, ostride = self._rows_view(out)
+        self._ok(self.mix.krk_head_linear(optr, ostride, int(out_col), float(out_scale), ptr, stride, w.data_ptr(), heads, N,
+                                          K, x.shape[0], _code(x.dtype), self._stream()), "per-head product")
+        return out
+
+    # -- routed experts ------------------------------------------------------------------------
+    MOE_PAIR_ROWS = 16  # rows up to which every (row, expert) pair reads its expert's weights by itself
+
+    def moe_route(self, x, w, b, top):
+        """(experts int32 [rows, top], weights float32 [rows, top]): the ``top`` largest of x W^T + b in 32-bit
+        (ties: the lower index) and the softmax over them."""
+        logits = self.linear(x, w, out_float32=True)
+        rows, E = logits.shape
+        experts = torch.empty((rows, top), dtype=torch.int32, device=x.device)
+        weights = torch.empty((rows, top), dtype=torch.float32, device=x.device)
+        self._ok(self.moe.krk_moe_route(experts.data_ptr(), weights.data_ptr(), logits.data_ptr(), _ptr(b), rows, E, int(top),
+                                        self._stream()), "expert routing")
+        return experts, weights
+
+    def moe_experts(self, x, w_gate_up, w_down, experts, weights, intermediate, activation, add=None, batch=None):
+        """add + sum_j weights[r, j] * expert_{experts[r, j]}(x[r]); w_gate_up [E, 2F, K], w_down [E, C, F]."""
+        rows, top = experts.shape
+        E, C, F = w_down.shape
+        K = x.shape[1]
+        ptr, stride = self._rows_view(x)
+        out = torch.empty((rows, C), dtype=x.dtype, device=x.device)
+        act = _ACTIVATIONS[activation]
+        single = batch is not None and batch.is_decode  # such a step may be replayed from a graph: nothing comes to the host
+        if single or rows * top <= max(self.MOE_PAIR_ROWS * top, 2 * E):
+            pairs = torch.empty((rows * top, F), dtype=x.dtype, device=x.device)
+            self._ok(self.moe.krk_moe_gate_up_pairs(pairs.data_ptr(), ptr, stride, w_gate_up.data_ptr(), experts.data_ptr(),
+                                                    rows, top, F, K, act, _code(x.dtype), self._stream()), "experts' gate/up")
+            self._ok(self.moe.krk_moe_down_pairs(out.data_ptr(), _ptr(add), pairs.data_ptr(), w_down.data_ptr(),
+                                                 experts.data_ptr(), weights.data_ptr(), rows, top, C, F, _code(x.dtype),
+                                                 self._stream()), "experts' down")
+            return out
+        # many rows: ordered by expert on the device; the experts' row ranges come to the host (a step of many
+        # tokens is never replayed from a graph), and each expert's rows go through the dense products
+        offsets = torch.empty(E + 1, dtype=torch.int32, device=x.device)
+        place = torch.empty(rows * top, dtype=torch.int32, device=x.device)
+        xg = torch.empty((rows * top, K), dtype=x.dtype, device=x.device)
+        self._ok(self.moe.krk_moe_sort(offsets.data_ptr(), place.data_ptr(), xg.data_ptr(), ptr, stride, experts.data_ptr(),
+                                       rows, top, E, K, _code(x.dtype), self._stream()), "expert ordering")
+        bounds = offsets.tolist()
+        yg = torch.empty((rows * top, C), dtype=x.dtype, device=x.device)
+        for e in range(E):
+            a, b = bounds[e], bounds[e + 1]
+            if b > a:
+                h = self.gate_up_act(xg[a:b], w_gate_up[e], F, activation)
+                yg[a:b] = self.linear(h, w_down[e])
+        self._ok(self.moe.krk_moe_combine(out.data_ptr(), _ptr(add), yg.data_ptr(), place.data_ptr(), weights.data_ptr(),
+                                          rows, top, C, _code(x.dtype), self._stream()), "experts' sum")
         return out
 
     def gate_up_act(self, h, w_gate_up, intermediate, activation):
@@ -506,17 +612,24 @@ class Kernels:
         return self.gated_act(self.linear(h, w_gate_up), intermediate, activation)
 
     def rotate_norm_write(self, proj, q_col, k_col, v_col, heads, kv_heads, dim, vdim, inv_freq, rot_dims, value_eps,
-                          batch, cache):
+                          batch, cache, value_mix=None):
         """Rotate q in place, rotate k into the cache, write v (divided by its root mean square if
-        ``value_eps`` is a number) into the cache; columns are offsets into ``proj``'s rows."""
+        ``value_eps`` is a number) into the cache; columns are offsets into ``proj``'s rows. ``value_mix``
+        (v_first rows, lambda): (1 - lambda) v + lambda v_first is what is written."""
         ptr, stride = self._rows_view(proj)
         if cache.k.dtype != proj.dtype or cache.head_dim != dim or cache.v_dim != vdim or cache.kv_heads != kv_heads:
             raise KernelError("the cache does not fit the heads it is to receive")
+        mix_ptr, mix_stride, lam = None, 0, 0.0
+        if value_mix is not None:
+            if value_eps is not None or value_mix[0].dtype != proj.dtype or value_mix[0].shape != (proj.shape[0], kv_heads * vdim):
+                raise KernelError("blended values come without a value norm, in the path's dtype, one row per row of the step")
+            (mix_ptr, mix_stride), lam = self._rows_view(value_mix[0]), float(value_mix[1])
         self._ok(self.mix.krk_rotate_norm_write(
             ptr, stride, q_col, k_col, v_col, heads, kv_heads, dim, vdim, inv_freq.data_ptr(), rot_dims,
             int(value_eps is not None), float(value_eps or 0.0), batch.row_seq.data_ptr(), batch.row_pos.data_ptr(),
             batch.seq_slot.data_ptr(), cache.table.data_ptr(), cache.width, cache.k.data_ptr(), cache.v.data_ptr(),
-            proj.shape[0], _code(proj.dtype), self._stream()), "rotation + value norm + cache write")
+            proj.shape[0], int(getattr(cache, "keep_pages", 0)), mix_ptr, mix_stride, lam, _code(proj.dtype),
+            self._stream()), "rotation + value norm + cache write")
 
     def sink_attention_step(self, proj, q_col, k_col, v_col, heads, kv_heads, dim, vdim, inv_freq, rot_dims, value_eps, sink,
                             scale, window, batch, cache, out, out_col, out_scale) -> bool:
@@ -530,9 +643,21 @@ class Kernels:
                                    fuse=(k_col, v_col, inv_freq, rot_dims, value_eps))
 
     def sink_attention(self, proj, q_col, heads, dim, vdim, sink, scale, window, batch, cache, out, out_col, out_scale,
-                       fuse=None):
+                       fuse=None, keep_first=0, gate=None, gate_rows=None):
+        """``keep_first``: a windowed query also sees the sequence's first keys. ``gate`` (column, "head" or "element"):
+        the result is multiplied by the sigmoid of those columns of ``gate_rows`` (default: of ``proj``)."""
         ptr, stride = self._rows_view(proj)
         optr, ostride = self._rows_view(out)
+        keep_first = int(keep_first) if window else 0
+        keep_pages = int(getattr(cache, "keep_pages", 0))
+        g_ptr, g_stride, g_col, g_mode = None, 0, 0, 0
+        if gate is not None:
+            g_rows = proj if gate_rows is None else gate_rows
+            if g_rows.dtype != proj.dtype or g_rows.shape[0] != proj.shape[0]:
+                raise KernelError("the gate's rows have the queries' dtype and number")
+            (g_ptr, g_stride), g_col, g_mode = self._rows_view(g_rows), int(gate[0]), {"head": 1, "element": 2}[gate[1]]
+        extras = (keep_first, keep_pages, g_ptr, g_stride, g_col, g_mode)
+        plain = not (keep_first or keep_pages or g_mode)
         if batch.is_decode and proj.shape[0] == batch.n_seqs:
             # one token per sequence: a block per (sequence, kv head), its warps splitting the window's keys. The
             # choice depends on the step's shape alone, so a sequence's results do not depend on its batch
@@ -551,7 +676,7 @@ class Kernels:
                 cache.k.data_ptr(), cache.v.data_ptr(), batch.n_seqs, float(scale), int(window or 0), splits,
                 _ptr(scratch), *((1, fuse[0], fuse[1], fuse[2].data_ptr(), fuse[3], int(fuse[4] is not None),
                                   float(fuse[4] or 0.0)) if fuse else (0, 0, 0, None, 0, 0, 0.0)),
-                _code(proj.dtype), self._stream())
+                *extras, _code(proj.dtype), self._stream())
             if rc != -2:  # -2: heads too large for it; the general kernel takes them
                 self._ok(rc, "single-token windowed attention with a sink")
                 return True
@@ -559,7 +684,7 @@ class Kernels:
                 return False
         elif fuse:
             return False
-        if (proj.dtype == torch.bfloat16 and dim == vdim and dim % 16 == 0 and dim <= 256 and dim in self.attn
+        if (plain and proj.dtype == torch.bfloat16 and dim == vdim and dim % 16 == 0 and dim <= 256 and dim in self.attn
                 and not batch.is_decode and hasattr(self.attn[dim], "krk_sink_window_prefill")):
             # many tokens per sequence in bfloat16: the tensor-core walk over whole pages (compiled per head size)
             esz = proj.element_size()
@@ -575,14 +700,14 @@ class Kernels:
             optr, ostride, out_col, float(out_scale), ptr, stride, q_col, heads, cache.kv_heads, dim, vdim, _ptr(sink),
             batch.row_seq.data_ptr(), batch.row_pos.data_ptr(), batch.seq_slot.data_ptr(), cache.table.data_ptr(),
             cache.width, cache.k.data_ptr(), cache.v.data_ptr(), proj.shape[0], float(scale), int(window or 0),
-            _code(proj.dtype), self._stream()), "windowed attention with a sink")
+            *extras, _code(proj.dtype), self._stream()), "windowed attention with a sink")
 
     def token_shift(self, h, last_state, mu, batch):
         """[mixes, rows, hidden]: h + (h_prev - h) * mu, the row before a step's first coming from ``last_state``."""
         ptr, stride = self._rows_view(h)
         rows, C = h.shape
         out = torch.empty((mu.shape[0], rows, C), dtype=h.dtype, device=h.device)
-        self._ok(self.mix.krk_token_shift(out.data_ptr(), ptr, stride, last_state.data_ptr(), mu.data_ptr(), mu.shape[0],
+        self._ok(self.scan.krk_token_shift(out.data_ptr(), ptr, stride, last_state.data_ptr(), mu.data_ptr(), mu.shape[0],
                                           C, rows, batch.row_seq.data_ptr(), batch.cu_q.data_ptr(),
                                           batch.seq_slot.data_ptr(), _code(h.dtype), self._stream()), "token shift")
         return out
@@ -605,7 +730,7 @@ class Kernels:
             # steps of many tokens: decays and gates over all rows at once, the scan between them (float32 scratch)
             prep = torch.empty(rows * heads * 6 * dim, dtype=torch.float32, device=r.device)
             o_raw = torch.empty(rows * heads * dim, dtype=torch.float32, device=r.device)
-        rc = self.mix.krk_linear_recurrence(
+        rc = self.scan.krk_linear_recurrence(
             {"wkv": 0, "delta": 1}[kind], views[0][0], views[0][1], views[1][0], views[1][1], views[2][0], views[2][1],
             views[3][0], views[3][1], rate_v[0], rate_v[1], lora_v[0], lora_v[1], w2.data_ptr(), w0.data_ptr(),
             _ptr(rate_bias), _ptr(bonus), norm_w.data_ptr(), state.data_ptr(), last_ptr, last_stride, C,

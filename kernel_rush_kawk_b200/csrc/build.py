@@ -1,10 +1,12 @@
 """Compiles this package's CUDA sources for sm_100a into shared libraries.
 
-Three kinds of library: ``core`` (kernels whose sizes are run-time arguments),
+Kinds of library: ``core`` (kernels whose sizes are run-time arguments),
 ``attn_d<D>`` (the attention kernels, compiled once per head size D with
-``-DKRK_HEAD_DIM=D``, so a model compiles only the head size it has) and ``mix``
+``-DKRK_HEAD_DIM=D``, so a model compiles only the head size it has), ``mix``
 (the kernels of models with a 32-bit residual stream, windowed attention with a
-sink and recurrent state; loaded by the first model that has such a part). A library
+sink or over latent rows), ``scan`` (recurrent state) and ``moe`` (routed
+experts); each of the last three is compiled and loaded when a model first calls
+one of its kernels, so a model compiles what it needs. A library
 is rebuilt when a source or a flag changes (its name carries a hash of both) and
 is otherwise loaded as it is. Libraries live in ``csrc/_build`` inside the
 package when that is writable, else under ``$KRK_BUILD_DIR`` or a per-user
@@ -30,7 +32,10 @@ SRC_DIR = Path(__file__).parent
 
 CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_simple.cu", "select.cu", "skinny_bf16.cu", "gemm_tcgen05.cu", "lt_gemm.cu"]
 CORE_LIBS = ["-lcublasLt"]  # lt_gemm.cu; the process already holds the copy that torch loaded
-MIX_SOURCES = ["wide_rows.cu", "sink_attention.cu", "recurrent.cu"]
+MIX_SOURCES = ["wide_rows.cu", "sink_attention.cu", "latent.cu"]
+SCAN_SOURCES = ["recurrent.cu"]
+MOE_SOURCES = ["routed.cu"]
+SMALL_LIBRARIES = {"mix": MIX_SOURCES, "scan": SCAN_SOURCES, "moe": MOE_SOURCES}
 ATTN_SOURCES = ["attention_simple.cu", "attention_mma.cu", "attention_tcgen05.cu"]
 HEADERS = ["common.cuh", "mma.cuh", "tcgen05.cuh", "attention_noalloc.h"]
 
@@ -91,8 +96,8 @@ def _key(sources, defines, libs=None) -> str:
 def library_path(kind: str, head_dim: int | None = None) -> tuple[Path, list, list]:
     if kind == "core":
         sources, defines, stem = _existing(CORE_SOURCES), [], "libkrk_core"
-    elif kind == "mix":
-        sources, defines, stem = _existing(MIX_SOURCES), [], "libkrk_mix"
+    elif kind in SMALL_LIBRARIES:
+        sources, defines, stem = _existing(SMALL_LIBRARIES[kind]), [], f"libkrk_{kind}"
         return build_dir() / f"{stem}_{_key(sources, defines, [])}.so", sources, defines
     else:
         sources, defines, stem = _existing(ATTN_SOURCES), [f"-DKRK_HEAD_DIM={int(head_dim)}"], f"libkrk_attn_d{int(head_dim)}"
@@ -161,7 +166,7 @@ def build_library(kind: str, head_dim: int | None = None, verbose: bool = True) 
 
 def build_all(head_dims=(16, 32, 64, 128), verbose: bool = True) -> list[Path]:
     """Compile the core library and the attention library of every given head size."""
-    out = [build_library("core", verbose=verbose), build_library("mix", verbose=verbose)]
+    out = [build_library("core", verbose=verbose)] + [build_library(kind, verbose=verbose) for kind in SMALL_LIBRARIES]
     for d in head_dims:
         out.append(build_library("attn", d, verbose=verbose))
     return out

@@ -146,3 +146,11 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 __device__ __forceinline__ int page_of(const int* __restrict__ table, int width, int slot, int pos) {
   return table[(size_t)slot * width + (pos / KRK_PAGE) % width];
 }
+
+// The same for a group whose first `keep` table entries hold the sequence's first pages for good while the
+// later pages cycle through the other entries.
+__device__ __forceinline__ int page_of(const int* __restrict__ table, int width, int slot, int pos, int keep) {
+  const int b = pos / KRK_PAGE;
+  const int e = b < keep ? b : keep + (b - keep) % max(width - keep, 1);
+  return table[(size_t)slot * width + e];
+}

@@ -1,0 +1,229 @@
+// Kernels of a feed-forward of routed experts.
+//
+// krk_moe_route: one warp per row. z = logits[r, :] + bias (float32); the `top` largest are taken one after
+// the other (ties: the lower index), and their weights are the softmax over the chosen logits alone.
+//
+// Few rows (single-token steps): a (row, chosen expert) pair reads its expert's weights once.
+//   krk_moe_gate_up_pairs: act[pair, f] = a(Wg_e[f] . x_r) * (Wu_e[f] . x_r), a warp per f, lanes over K.
+//   krk_moe_down_pairs: out[r, c] = add[r, c] + sum_j weight[r, j] * (Wd_e(j)[c] . act[(r, j)]), a warp per c;
+//   the sum over the chosen experts is float32, in the order of the choice.
+//
+// Many rows: pairs are counted per expert and ordered by expert on the device (krk_moe_sort: one block; offsets,
+// the pairs' places and the rows gathered in that order), the experts' products run over contiguous rows, and
+// krk_moe_combine adds each row's weighted results onto `add`.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float act_of(float z, int act) {
+  if (act == 0) return z / (1.0f + expf(-z));
+  if (act == 1) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return 1.0f / (1.0f + expf(-z));
+}
+
+constexpr int ROUTE_WARPS = 4;
+
+__global__ void moe_route_kernel(int* __restrict__ experts, float* __restrict__ weights, const float* __restrict__ logits,
+                                 const float* __restrict__ bias, int rows, int E, int top) {
+  extern __shared__ float z_s[];  // [warps][E]
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x * ROUTE_WARPS + warp;
+  if (row >= rows) return;
+  float* z = z_s + (size_t)warp * E;
+  for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)row * E + e] + (bias ? bias[e] : 0.f);
+  __syncwarp();
+  float first = 0.f, total = 0.f, mine = 0.f;
+  int mine_e = 0;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best) { best = v; best_e = e; }  // ascending e: the lower index stays on a tie
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+    }
+    if (j == 0) first = best;
+    const float p = expf(best - first);
+    total += p;
+    if (lane == j) { mine = p; mine_e = best_e; }
+    if (lane == 0) z[best_e] = -INFINITY;
+    __syncwarp();
+  }
+  if (lane < top) {
+    experts[(size_t)row * top + lane] = mine_e;
+    weights[(size_t)row * top + lane] = mine / total;
+  }
+}
+
+constexpr int PAIR_WARPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(PAIR_WARPS * 32)
+moe_gate_up_pairs_kernel(T* __restrict__ act_out, const T* __restrict__ x, int x_stride, const T* __restrict__ w,
+                         const int* __restrict__ experts, int top, int F, int K, int act) {
+  extern __shared__ float xs[];  // [K]
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pair = blockIdx.y;
+  const int e = experts[pair];
+  const T* xr = x + (size_t)(pair / top) * x_stride;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float<T>(xr[k]);
+  __syncthreads();
+  const T* we = w + (size_t)e * 2 * F * K;
+  for (int f = blockIdx.x * PAIR_WARPS + warp; f < F; f += gridDim.x * PAIR_WARPS) {
+    const T* wg = we + (size_t)f * K;
+    const T* wu = we + (size_t)(F + f) * K;
+    float g = 0.f, u = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const float xv = xs[k];
+      g += to_float<T>(wg[k]) * xv;
+      u += to_float<T>(wu[k]) * xv;
+    }
+    g = warp_sum(g);
+    u = warp_sum(u);
+    // the two products leave in the path's type before the activation, as they do from a product kernel
+    if (lane == 0) act_out[(size_t)pair * F + f] = from_float<T>(act_of(round_to<T>(g), act) * round_to<T>(u));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(PAIR_WARPS * 32)
+moe_down_pairs_kernel(T* __restrict__ out, const T* __restrict__ add, const T* __restrict__ act_in,
+                      const T* __restrict__ w, const int* __restrict__ experts, const float* __restrict__ weights, int top,
+                      int C, int F) {
+  extern __shared__ float as[];  // [top][F]
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.y;
+  for (int i = threadIdx.x; i < top * F; i += blockDim.x) as[i] = to_float<T>(act_in[(size_t)row * top * F + i]);
+  __syncthreads();
+  for (int c = blockIdx.x * PAIR_WARPS + warp; c < C; c += gridDim.x * PAIR_WARPS) {
+    float total = add ? to_float<T>(add[(size_t)row * C + c]) : 0.f;
+    for (int j = 0; j < top; ++j) {
+      const int e = experts[(size_t)row * top + j];
+      const T* wr = w + ((size_t)e * C + c) * F;
+      float s = 0.f;
+      for (int k = lane; k < F; k += 32) s += to_float<T>(wr[k]) * as[j * F + k];
+      s = warp_sum(s);
+      total += weights[(size_t)row * top + j] * round_to<T>(s);
+    }
+    if (lane == 0) out[(size_t)row * C + c] = from_float<T>(total);
+  }
+}
+
+// One block: counts per expert, offsets, each pair's place in the expert order (stable: pairs of one expert
+// keep their order), and the rows of x gathered in that order.
+__global__ void moe_sort_kernel(int* __restrict__ offsets, int* __restrict__ place, const int* __restrict__ experts,
+                                int pairs, int E) {
+  extern __shared__ int cnt[];  // [E + 1]
+  grid_dependency_wait();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&cnt[experts[i] + 1], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int e = 0; e < E; ++e) cnt[e + 1] += cnt[e];
+    for (int e = 0; e <= E; ++e) offsets[e] = cnt[e];
+  }
+  __syncthreads();
+  // a thread per expert walks the pairs in order: stable, and E is small beside the pairs' work that follows
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int at = cnt[e];
+    for (int i = 0; i < pairs; ++i)
+      if (experts[i] == e) place[i] = at++;
+  }
+}
+
+template <typename T>
+__global__ void moe_gather_kernel(T* __restrict__ xg, const T* __restrict__ x, int x_stride, const int* __restrict__ place,
+                                  int top, int K) {
+  grid_dependency_wait();
+  const int pair = blockIdx.x;
+  const T* src = x + (size_t)(pair / top) * x_stride;
+  T* dst = xg + (size_t)place[pair] * K;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = src[k];
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ add, const T* __restrict__ yg,
+                                   const int* __restrict__ place, const float* __restrict__ weights, int top, int C) {
+  grid_dependency_wait();
+  const int row = blockIdx.x;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float total = add ? to_float<T>(add[(size_t)row * C + c]) : 0.f;
+    for (int j = 0; j < top; ++j)
+      total += weights[(size_t)row * top + j] * to_float<T>(yg[(size_t)place[(size_t)row * top + j] * C + c]);
+    out[(size_t)row * C + c] = from_float<T>(total);
+  }
+}
+
+}  // namespace
+
+KRK_API int krk_moe_route(int* experts, float* weights, const float* logits, const float* bias, int rows, int E, int top,
+                          cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (top < 1 || top > 32 || top > E) return -2;
+  const size_t smem = (size_t)ROUTE_WARPS * E * sizeof(float);
+  if (smem > 48 * 1024) return -2;
+  return (int)launch_pdl(moe_route_kernel, dim3((rows + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream,
+                         experts, weights, logits, bias, rows, E, top);
+}
+
+KRK_API int krk_moe_gate_up_pairs(void* act_out, const void* x, int x_stride, const void* w, const int* experts, int rows,
+                                  int top, int F, int K, int act, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  const size_t smem = (size_t)K * sizeof(float);
+  if (smem > 48 * 1024 || (long long)rows * top > 65535) return -2;
+  const dim3 grid((unsigned)min((F + PAIR_WARPS - 1) / PAIR_WARPS, 1024), (unsigned)(rows * top));
+  if (dtype == KRK_DTYPE_F32)
+    return (int)launch_pdl(moe_gate_up_pairs_kernel<float>, grid, dim3(PAIR_WARPS * 32), smem, stream, (float*)act_out,
+                           (const float*)x, x_stride, (const float*)w, experts, top, F, K, act);
+  return (int)launch_pdl(moe_gate_up_pairs_kernel<bf16>, grid, dim3(PAIR_WARPS * 32), smem, stream, (bf16*)act_out,
+                         (const bf16*)x, x_stride, (const bf16*)w, experts, top, F, K, act);
+}
+
+KRK_API int krk_moe_down_pairs(void* out, const void* add, const void* act_in, const void* w, const int* experts,
+                               const float* weights, int rows, int top, int C, int F, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  const size_t smem = (size_t)top * F * sizeof(float);
+  if (smem > 48 * 1024 || rows > 65535) return -2;
+  const dim3 grid((unsigned)min((C + PAIR_WARPS - 1) / PAIR_WARPS, 1024), (unsigned)rows);
+  if (dtype == KRK_DTYPE_F32)
+    return (int)launch_pdl(moe_down_pairs_kernel<float>, grid, dim3(PAIR_WARPS * 32), smem, stream, (float*)out,
+                           (const float*)add, (const float*)act_in, (const float*)w, experts, weights, top, C, F);
+  return (int)launch_pdl(moe_down_pairs_kernel<bf16>, grid, dim3(PAIR_WARPS * 32), smem, stream, (bf16*)out,
+                         (const bf16*)add, (const bf16*)act_in, (const bf16*)w, experts, weights, top, C, F);
+}
+
+KRK_API int krk_moe_sort(int* offsets, int* place, void* xg, const void* x, int x_stride, const int* experts, int rows,
+                         int top, int E, int K, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  const int pairs = rows * top;
+  cudaError_t e = launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(E + 1) * sizeof(int), stream, offsets, place,
+                             experts, pairs, E);
+  if (e != cudaSuccess) return (int)e;
+  if (dtype == KRK_DTYPE_F32)
+    return (int)launch_pdl(moe_gather_kernel<float>, dim3(pairs), dim3(128), 0, stream, (float*)xg, (const float*)x,
+                           x_stride, (const int*)place, top, K);
+  return (int)launch_pdl(moe_gather_kernel<bf16>, dim3(pairs), dim3(128), 0, stream, (bf16*)xg, (const bf16*)x, x_stride,
+                         (const int*)place, top, K);
+}
+
+KRK_API int krk_moe_combine(void* out, const void* add, const void* yg, const int* place, const float* weights, int rows,
+                            int top, int C, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (dtype == KRK_DTYPE_F32)
+    return (int)launch_pdl(moe_combine_kernel<float>, dim3(rows), dim3(256), 0, stream, (float*)out, (const float*)add,
+                           (const float*)yg, place, weights, top, C);
+  return (int)launch_pdl(moe_combine_kernel<bf16>, dim3(rows), dim3(256), 0, stream, (bf16*)out, (const bf16*)add,
+                         (const bf16*)yg, place, weights, top, C);
+}

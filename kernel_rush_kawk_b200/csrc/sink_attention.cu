@@ -22,11 +22,19 @@
 // warps' running (maximum, sum, output) are merged in warp order at the end; the sink enters once, as
 // the first warp's starting state. Where few (sequence, kv head) items would leave most SMs idle, several
 // blocks share an item's chunks and a small kernel merges their results in block order.
+//
+// Options of all three: the cache may keep a sequence's first pages for good (`keep_pages`, see page_of); a
+// windowed query may also see the first `keep_first` keys (they are walked before the window's own, in position
+// order); the result may be multiplied by sigmoid(gate), one number per head (mode 1) or per element (mode 2),
+// read from the columns `gate_col` of `gate`'s rows; the values that are written may be blended with another
+// layer's values of the same rows, (1 - lambda) v + lambda v_first.
 #include "common.cuh"
 
 namespace {
 
-constexpr int MAX_V_PER_LANE = 8;  // value heads up to 256
+constexpr int MAX_V_PER_LANE = 8;
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }  // value heads up to 256
 
 // sine and cosine of p * (f_hi + f_lo)
 __device__ __forceinline__ void angle_sincos(float p, float f_hi, float f_lo, float* s, float* c) {
@@ -43,7 +51,8 @@ __global__ void rotate_norm_write_kernel(T* proj, int stride, int q_col, int k_c
                                          int DV, const float* __restrict__ inv_freq, int rot, int value_norm, float eps,
                                          const int* __restrict__ row_seq, const int* __restrict__ row_pos,
                                          const int* __restrict__ seq_slot, const int* __restrict__ table, int width,
-                                         T* k_cache, T* v_cache, int rows) {
+                                         T* k_cache, T* v_cache, int rows, int keep_pages,
+                                         const T* __restrict__ mix_first, int mix_stride, float lam) {
   grid_launch_dependents();
   grid_dependency_wait();
   const int lane = threadIdx.x & 31;
@@ -67,7 +76,7 @@ __global__ void rotate_norm_write_kernel(T* proj, int stride, int q_col, int k_c
     return;
   }
   const int slot = seq_slot[row_seq[row]];
-  const int page = page_of(table, width, slot, pos);
+  const int page = page_of(table, width, slot, pos, keep_pages);
   if (which < HQ + HKV) {
     const int h = which - HQ;
     const T* k = src + k_col + (size_t)h * D;
@@ -85,6 +94,11 @@ __global__ void rotate_norm_write_kernel(T* proj, int stride, int q_col, int k_c
   const int h = which - HQ - HKV;
   const T* v = src + v_col + (size_t)h * DV;
   T* dst = v_cache + (((size_t)page * HKV + h) * KRK_PAGE + (pos % KRK_PAGE)) * DV;
+  if (mix_first) {  // blended with another layer's values of this row (no design has both a blend and a value norm)
+    const T* f = mix_first + (size_t)row * mix_stride + (size_t)h * DV;
+    for (int i = lane; i < DV; i += 32) dst[i] = from_float<T>((1.0f - lam) * to_float<T>(v[i]) + lam * to_float<T>(f[i]));
+    return;
+  }
   float rstd = 1.f;
   if (value_norm) {
     float sq = 0.f;
@@ -127,7 +141,9 @@ __global__ void sink_attention_kernel(T* __restrict__ out, int out_stride, int o
                                       const float* __restrict__ sink, const int* __restrict__ row_seq,
                                       const int* __restrict__ row_pos, const int* __restrict__ seq_slot,
                                       const int* __restrict__ table, int width, const T* __restrict__ k_cache,
-                                      const T* __restrict__ v_cache, int rows, float scale, int window) {
+                                      const T* __restrict__ v_cache, int rows, float scale, int window, int keep_first,
+                                      int keep_pages, const T* __restrict__ gate, int gate_stride, int gate_col,
+                                      int gate_mode) {
   extern __shared__ float q_s[];  // warps x D
   grid_launch_dependents();
   grid_dependency_wait();
@@ -151,21 +167,25 @@ __global__ void sink_attention_kernel(T* __restrict__ out, int out_stride, int o
 #pragma unroll
   for (int i = 0; i < MAX_V_PER_LANE; ++i) acc[i] = 0.f;
 
-  for (int base = first; base <= pos; base += 32) {
+  // the kept first keys that the window no longer covers, then the window's own
+  const int kept_hi = (window > 0 && keep_first > 0) ? min(keep_first, first) - 1 : -1;
+  for (int seg = 0; seg < 2; ++seg) {
+  const int lo = seg ? first : 0, hi = seg ? pos : kept_hi;
+  for (int base = lo; base <= hi; base += 32) {
     const int key = base + lane;
     float s = -INFINITY;
     int my_page = 0;
-    if (key <= pos) {
-      my_page = page_of(table, width, slot, key);
+    if (key <= hi) {
+      my_page = page_of(table, width, slot, key, keep_pages);
       s = dot_row<T>(qs, k_cache + (((size_t)my_page * HKV + kh) * KRK_PAGE + (key % KRK_PAGE)) * D, D) * scale;
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float alpha = expf(m - m_new);  // exp(-inf) = 0 before the first key when there is no sink
-    const float p = key <= pos ? expf(s - m_new) : 0.f;
+    const float p = key <= hi ? expf(s - m_new) : 0.f;
     l = l * alpha + warp_sum(p);
 #pragma unroll
     for (int i = 0; i < MAX_V_PER_LANE; ++i) acc[i] *= alpha;
-    const int n = min(32, pos - base + 1);
+    const int n = min(32, hi - base + 1);
 #pragma unroll 4
     for (int j = 0; j < n; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
@@ -180,12 +200,15 @@ __global__ void sink_attention_kernel(T* __restrict__ out, int out_stride, int o
     }
     m = m_new;
   }
+  }
   T* o = out + (size_t)row * out_stride + out_col + (size_t)head * DV;
-  const float inv = out_scale / l;
+  float inv = out_scale / l;
+  const T* gp = gate_mode ? gate + (size_t)row * gate_stride + gate_col : nullptr;
+  if (gate_mode == 1) inv *= sigmoidf_(to_float<T>(gp[head]));
 #pragma unroll
   for (int i = 0; i < MAX_V_PER_LANE; ++i) {
     const int d = lane + 32 * i;
-    if (d < DV) o[d] = from_float<T>(acc[i] * inv);
+    if (d < DV) o[d] = from_float<T>(acc[i] * inv * (gate_mode == 2 ? sigmoidf_(to_float<T>(gp[(size_t)head * DV + d])) : 1.f));
   }
 }
 
@@ -228,7 +251,8 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
                              const T* __restrict__ k_cache, const T* __restrict__ v_cache, float scale, int window,
                              int g0, int GN, int SPL, float* __restrict__ scratch, int k_col, int v_col,
                              const float* __restrict__ inv_freq, int rot, int value_norm, float eps, T* k_cache_w,
-                             T* v_cache_w) {
+                             T* v_cache_w, int keep_first, int keep_pages, const T* __restrict__ gate, int gate_stride,
+                             int gate_col, int gate_mode) {
   extern __shared__ __align__(16) float sm1[];
   float* q_s = sm1;                       // [GN][D]
   float* part = q_s + GN * D;             // [warps][GN][DV + 2]
@@ -288,7 +312,7 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
     for (int j = threadIdx.x; j < DV; j += blockDim.x) vn[j] = from_float<T>(to_float<T>(vr[j]) * rstd_s);
     __syncthreads();
     if (split == 0) {
-      const int page = page_of(table, width, slot, pos);
+      const int page = page_of(table, width, slot, pos, keep_pages);
       T* kd = k_cache_w + (((size_t)page * HKV + kh) * KRK_PAGE + (pos % KRK_PAGE)) * D;
       T* vd = v_cache_w + (((size_t)page * HKV + kh) * KRK_PAGE + (pos % KRK_PAGE)) * DV;
       for (int j = threadIdx.x; j < D; j += blockDim.x) kd[j] = kn[j];
@@ -306,14 +330,19 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
     for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) acc[g][i] = 0.f;
   }
   const bool vec = (D & 7) == 0;  // rows of the cache then start on 16-byte boundaries (32 for float)
-  for (int base = first + 32 * (split + SPL * warp); base <= pos; base += 32 * SPL * SINGLE_WARPS) {
+  // the kept first keys that the window no longer covers, then the window's own; chunks of either go round the
+  // item's blocks and warps
+  const int kept_hi = (window > 0 && keep_first > 0) ? min(keep_first, first) - 1 : -1;
+  for (int seg = 0; seg < 2; ++seg) {
+  const int lo = seg ? first : 0, hi = seg ? pos : kept_hi;
+  for (int base = lo + 32 * (split + SPL * warp); base <= hi; base += 32 * SPL * SINGLE_WARPS) {
     const int key = base + lane;
     float s[GROUP_MAX];
 #pragma unroll
     for (int g = 0; g < GROUP_MAX; ++g) s[g] = 0.f;
     int my_page = 0;
-    if (key <= pos) {
-      my_page = page_of(table, width, slot, key);
+    if (key <= hi) {
+      my_page = page_of(table, width, slot, key, keep_pages);
       const T* kp = (FUSE && key == pos) ? kn  // the new token's key is not in its page for every block yet
                                          : k_cache + (((size_t)my_page * HKV + kh) * KRK_PAGE + (key % KRK_PAGE)) * D;
       if (vec) {
@@ -360,16 +389,16 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
 #pragma unroll
     for (int g = 0; g < GROUP_MAX; ++g) {
       if (g >= GN) continue;
-      const float sc = key <= pos ? s[g] * scale : -INFINITY;
+      const float sc = key <= hi ? s[g] * scale : -INFINITY;
       const float m_new = fmaxf(m[g], warp_max(sc));
       const float alpha = expf(m[g] - m_new);
-      p[g] = key <= pos ? expf(sc - m_new) : 0.f;
+      p[g] = key <= hi ? expf(sc - m_new) : 0.f;
       l[g] = l[g] * alpha + warp_sum(p[g]);
 #pragma unroll
       for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) acc[g][i] *= alpha;
       m[g] = m_new;
     }
-    const int n = min(32, pos - base + 1);
+    const int n = min(32, hi - base + 1);
     for (int j0 = 0; j0 < n; j0 += 16) {  // sixteen value rows are requested before the first is used
       float vf[16][MAX_V_PER_LANE / 2];
 #pragma unroll
@@ -398,6 +427,7 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
           for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) acc[g][i] += pj * vf[jj][i];
         }
     }
+  }
   }
   // the warps' partial results, then one warp per head merges them in warp order
   const int PS = DV + 2;
@@ -440,11 +470,14 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
       continue;
     }
     T* op = out + (size_t)seq * out_stride + out_col + (size_t)(head0 + g) * DV;
-    const float inv = out_scale / total;
+    float inv = out_scale / total;
+    const T* gp = gate_mode ? gate + (size_t)seq * gate_stride + gate_col : nullptr;
+    if (gate_mode == 1) inv *= sigmoidf_(to_float<T>(gp[head0 + g]));
 #pragma unroll
     for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) {
       const int d = V4 ? 4 * lane + i : lane + 32 * i;
-      if (d < DV) op[d] = from_float<T>(o[i] * inv);
+      if (d < DV)
+        op[d] = from_float<T>(o[i] * inv * (gate_mode == 2 ? sigmoidf_(to_float<T>(gp[(size_t)(head0 + g) * DV + d])) : 1.f));
     }
   }
 }
@@ -453,7 +486,8 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
 template <typename T>
 __global__ void sink_attention_merge_kernel(T* __restrict__ out, int out_stride, int out_col, float out_scale,
                                             const float* __restrict__ scratch, int HQ, int HKV, int DV, int SPL,
-                                            int n_items) {
+                                            int n_items, const T* __restrict__ gate, int gate_stride, int gate_col,
+                                            int gate_mode) {
   grid_launch_dependents();
   grid_dependency_wait();
   const int lane = threadIdx.x & 31;
@@ -478,11 +512,14 @@ __global__ void sink_attention_merge_kernel(T* __restrict__ out, int out_stride,
     }
   }
   T* op = out + (size_t)seq * out_stride + out_col + (size_t)(kh * G + g) * DV;
-  const float inv = out_scale / total;
+  float inv = out_scale / total;
+  const T* gp = gate_mode ? gate + (size_t)seq * gate_stride + gate_col : nullptr;
+  if (gate_mode == 1) inv *= sigmoidf_(to_float<T>(gp[kh * G + g]));
 #pragma unroll
   for (int i = 0; i < MAX_V_PER_LANE; ++i) {
     const int d = lane + 32 * i;
-    if (d < DV) op[d] = from_float<T>(o[i] * inv);
+    if (d < DV)
+      op[d] = from_float<T>(o[i] * inv * (gate_mode == 2 ? sigmoidf_(to_float<T>(gp[(size_t)(kh * G + g) * DV + d])) : 1.f));
   }
 }
 
@@ -491,7 +528,8 @@ __global__ void sink_attention_merge_kernel(T* __restrict__ out, int out_stride,
 KRK_API int krk_rotate_norm_write(void* proj, int stride, int q_col, int k_col, int v_col, int HQ, int HKV, int D, int DV,
                                   const float* inv_freq, int rot, int value_norm, float eps, const int* row_seq,
                                   const int* row_pos, const int* seq_slot, const int* table, int width, void* k_cache,
-                                  void* v_cache, int rows, int dtype, cudaStream_t stream) {
+                                  void* v_cache, int rows, int keep_pages, const void* mix_first, int mix_stride,
+                                  float lam, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (rot < 0 || rot > D || (rot & 1)) return -2;
   const long long items = (long long)rows * (HQ + 2 * HKV);
@@ -501,16 +539,20 @@ KRK_API int krk_rotate_norm_write(void* proj, int stride, int q_col, int k_col, 
   if (dtype == KRK_DTYPE_F32)
     return (int)launch_pdl(rotate_norm_write_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
                            (float*)proj, stride, q_col, k_col, v_col, HQ, HKV, D, DV, inv_freq, rot, value_norm, eps,
-                           row_seq, row_pos, seq_slot, table, width, (float*)k_cache, (float*)v_cache, rows);
+                           row_seq, row_pos, seq_slot, table, width, (float*)k_cache, (float*)v_cache, rows, keep_pages,
+                           (const float*)mix_first, mix_stride, lam);
   return (int)launch_pdl(rotate_norm_write_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, (bf16*)proj,
                          stride, q_col, k_col, v_col, HQ, HKV, D, DV, inv_freq, rot, value_norm, eps, row_seq, row_pos,
-                         seq_slot, table, width, (bf16*)k_cache, (bf16*)v_cache, rows);
+                         seq_slot, table, width, (bf16*)k_cache, (bf16*)v_cache, rows, keep_pages, (const bf16*)mix_first,
+                         mix_stride, lam);
 }
 
 KRK_API int krk_sink_attention(void* out, int out_stride, int out_col, float out_scale, const void* proj, int stride,
                                int q_col, int HQ, int HKV, int D, int DV, const float* sink, const int* row_seq,
                                const int* row_pos, const int* seq_slot, const int* table, int width, const void* k_cache,
-                               const void* v_cache, int rows, float scale, int window, int dtype, cudaStream_t stream) {
+                               const void* v_cache, int rows, float scale, int window, int keep_first, int keep_pages,
+                               const void* gate, int gate_stride, int gate_col, int gate_mode, int dtype,
+                               cudaStream_t stream) {
   if (rows == 0) return 0;
   if (DV > 32 * MAX_V_PER_LANE || D > 2048) return -2;
   const long long items = (long long)rows * HQ;
@@ -522,10 +564,11 @@ KRK_API int krk_sink_attention(void* out, int out_stride, int out_col, float out
     return (int)launch_pdl(sink_attention_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream,
                            (float*)out, out_stride, out_col, out_scale, (const float*)proj, stride, q_col, HQ, HKV, D, DV,
                            sink, row_seq, row_pos, seq_slot, table, width, (const float*)k_cache, (const float*)v_cache,
-                           rows, scale, window);
+                           rows, scale, window, keep_first, keep_pages, (const float*)gate, gate_stride, gate_col, gate_mode);
   return (int)launch_pdl(sink_attention_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, (bf16*)out,
                          out_stride, out_col, out_scale, (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink, row_seq,
-                         row_pos, seq_slot, table, width, (const bf16*)k_cache, (const bf16*)v_cache, rows, scale, window);
+                         row_pos, seq_slot, table, width, (const bf16*)k_cache, (const bf16*)v_cache, rows, scale, window,
+                         keep_first, keep_pages, (const bf16*)gate, gate_stride, gate_col, gate_mode);
 }
 
 // One token per sequence: rows are the sequences, in order. Value heads of up to 128 elements; others take
@@ -538,7 +581,8 @@ KRK_API int krk_sink_attention_single(void* out, int out_stride, int out_col, fl
                                       const int* seq_start, const int* table, int width, const void* k_cache,
                                       const void* v_cache, int n_seqs, float scale, int window, int splits,
                                       float* scratch, int fuse, int k_col, int v_col, const float* inv_freq, int rot,
-                                      int value_norm, float eps, int dtype, cudaStream_t stream) {
+                                      int value_norm, float eps, int keep_first, int keep_pages, const void* gate,
+                                      int gate_stride, int gate_col, int gate_mode, int dtype, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   if (DV > 32 * (MAX_V_PER_LANE / 2) || D > 1024) return -2;
   const int G = HQ / HKV;
@@ -570,14 +614,16 @@ KRK_API int krk_sink_attention_single(void* out, int out_stride, int out_col, fl
                      dim3(n_seqs * HKV * SPL), dim3(SINGLE_WARPS * 32), smem, stream,
                      (float*)out, out_stride, out_col, out_scale, (const float*)proj, stride, q_col, HQ, HKV, D, DV, sink,
                      seq_slot, seq_start, table, width, (const float*)k_cache, (const float*)v_cache, scale, window, g0, GN, SPL, scratch, k_col, v_col,
-                     inv_freq, rot, value_norm, eps, (float*)k_cache, (float*)v_cache);
+                     inv_freq, rot, value_norm, eps, (float*)k_cache, (float*)v_cache, keep_first, keep_pages,
+                     (const float*)gate, gate_stride, gate_col, gate_mode);
     else
       e = launch_pdl(fuse ? (v4 ? sink_attention_single_kernel<bf16, true, true> : sink_attention_single_kernel<bf16, false, true>)
                           : (v4 ? sink_attention_single_kernel<bf16, true, false> : sink_attention_single_kernel<bf16, false, false>),
                      dim3(n_seqs * HKV * SPL), dim3(SINGLE_WARPS * 32), smem, stream,
                      (bf16*)out, out_stride, out_col, out_scale, (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink,
                      seq_slot, seq_start, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale, window, g0, GN, SPL, scratch, k_col, v_col,
-                     inv_freq, rot, value_norm, eps, (bf16*)k_cache, (bf16*)v_cache);
+                     inv_freq, rot, value_norm, eps, (bf16*)k_cache, (bf16*)v_cache, keep_first, keep_pages,
+                     (const bf16*)gate, gate_stride, gate_col, gate_mode);
     if (e != cudaSuccess) return (int)e;
   }
   if (SPL > 1) {
@@ -586,10 +632,12 @@ KRK_API int krk_sink_attention_single(void* out, int out_stride, int out_col, fl
     cudaError_t e;
     if (dtype == KRK_DTYPE_F32)
       e = launch_pdl(sink_attention_merge_kernel<float>, dim3(blocks), dim3(128), 0, stream, (float*)out, out_stride,
-                     out_col, out_scale, (const float*)scratch, HQ, HKV, DV, SPL, n_seqs * HKV);
+                     out_col, out_scale, (const float*)scratch, HQ, HKV, DV, SPL, n_seqs * HKV, (const float*)gate,
+                     gate_stride, gate_col, gate_mode);
     else
       e = launch_pdl(sink_attention_merge_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, (bf16*)out, out_stride,
-                     out_col, out_scale, (const float*)scratch, HQ, HKV, DV, SPL, n_seqs * HKV);
+                     out_col, out_scale, (const float*)scratch, HQ, HKV, DV, SPL, n_seqs * HKV, (const bf16*)gate,
+                     gate_stride, gate_col, gate_mode);
     if (e != cudaSuccess) return (int)e;
   }
   return 0;

@@ -2,9 +2,11 @@
 // embedding gather, RMSNorm over a float32 stream with the residual add folded in,
 // and the gated activation of a feed-forward with the activation as an argument.
 //
-// Norm: s = x + branch (float32, written out as the new stream); y = s * rsqrt(mean(s^2)
-// + eps) * (offset + w), rounded once to the element type T of the path. The gain is
-// float32. One block per row, the row held in shared memory, global memory read once.
+// Norm: s = x + m * (branch + branch2) (float32, written out as the new stream; the second
+// branch is optional and m is 1 for the usual add); y = s * rsqrt(mean(s^2) + eps) *
+// (offset + w), rounded once to the element type T of the path; a second gain gives a
+// second result from the same pass. The gains are float32. One block per row, the row
+// held in shared memory, global memory read once.
 #include "common.cuh"
 
 namespace {
@@ -47,7 +49,9 @@ template <> __device__ __forceinline__ void store4_rows<bf16>(bf16* p, const flo
 
 template <typename T, bool VEC>
 __global__ void rmsnorm_wide_kernel(T* __restrict__ out, float* x_new, const float* x, const T* __restrict__ branch,
-                                    const float* __restrict__ gain, float offset, int H, float eps) {
+                                    const float* __restrict__ gain, float offset, int H, float eps,
+                                    const T* __restrict__ branch2, float bscale, const float* __restrict__ gain2,
+                                    T* __restrict__ out2) {
   extern __shared__ __align__(16) float row_s[];  // H floats
   __shared__ float scratch[32];
   grid_launch_dependents();
@@ -62,7 +66,12 @@ __global__ void rmsnorm_wide_kernel(T* __restrict__ out, float* x_new, const flo
       if (branch) {
         float b[4];
         load4_rows<T>(branch + base + 4 * i, b);
-        f.x += b[0]; f.y += b[1]; f.z += b[2]; f.w += b[3];
+        if (branch2) {
+          float c[4];
+          load4_rows<T>(branch2 + base + 4 * i, c);
+          b[0] += c[0]; b[1] += c[1]; b[2] += c[2]; b[3] += c[3];
+        }
+        f.x += bscale * b[0]; f.y += bscale * b[1]; f.z += bscale * b[2]; f.w += bscale * b[3];
         nv[i] = f;
       }
       reinterpret_cast<float4*>(row_s)[i] = f;
@@ -72,7 +81,9 @@ __global__ void rmsnorm_wide_kernel(T* __restrict__ out, float* x_new, const flo
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float f = x[base + i];
       if (branch) {
-        f += to_float<T>(branch[base + i]);
+        float b = to_float<T>(branch[base + i]);
+        if (branch2) b += to_float<T>(branch2[base + i]);
+        f += bscale * b;
         x_new[base + i] = f;
       }
       row_s[i] = f;
@@ -87,10 +98,18 @@ __global__ void rmsnorm_wide_kernel(T* __restrict__ out, float* x_new, const flo
       const float r[4] = {f.x * rstd * (offset + g.x), f.y * rstd * (offset + g.y), f.z * rstd * (offset + g.z),
                           f.w * rstd * (offset + g.w)};
       store4_rows<T>(out + base + 4 * i, r);
+      if (gain2) {
+        const float4 h = reinterpret_cast<const float4*>(gain2)[i];
+        const float r2[4] = {f.x * rstd * (offset + h.x), f.y * rstd * (offset + h.y), f.z * rstd * (offset + h.z),
+                             f.w * rstd * (offset + h.w)};
+        store4_rows<T>(out2 + base + 4 * i, r2);
+      }
     }
   } else {
-    for (int i = threadIdx.x; i < H; i += blockDim.x)
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
       out[base + i] = from_float<T>(row_s[i] * rstd * (offset + gain[i]));
+      if (gain2) out2[base + i] = from_float<T>(row_s[i] * rstd * (offset + gain2[i]));
+    }
   }
 }
 
@@ -100,19 +119,22 @@ __device__ __forceinline__ float activation(float z, int act) {
   return 1.0f / (1.0f + expf(-z));                                                              // sigmoid
 }
 
-// out[r, i] = round(act(g) * u), g = gu[r, i], u = gu[r, I + i]
+// out[r, i] = round(act(g) * u), g = gu[r, i], u = gu[r, I + i]; with row_gate_col >= 0 the row is also
+// multiplied by sigmoid(gu[r, row_gate_col]) (a gate of one number per row that rides in the same product)
 template <typename T, bool VEC>
-__global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, int gu_stride, int I, int act) {
+__global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, int gu_stride, int I, int act,
+                                 int row_gate_col) {
   grid_launch_dependents();
   grid_dependency_wait();
   const size_t r = blockIdx.x;
+  const float rg = row_gate_col >= 0 ? activation(to_float<T>(gu[r * gu_stride + row_gate_col]), 2) : 1.f;
   if (VEC) {  // I and the row stride multiples of 4
     for (int i = 4 * (blockIdx.y * blockDim.x + threadIdx.x); i < I; i += 4 * gridDim.y * blockDim.x) {
       float g[4], u[4], o[4];
       load4_rows<T>(gu + r * gu_stride + i, g);
       load4_rows<T>(gu + r * gu_stride + I + i, u);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) o[j] = activation(g[j], act) * u[j];
+      for (int j = 0; j < 4; ++j) o[j] = activation(g[j], act) * u[j] * rg;
       store4_rows<T>(out + r * I + i, o);
     }
     return;
@@ -120,7 +142,7 @@ __global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, 
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
     const float g = to_float<T>(gu[r * gu_stride + i]);
     const float u = to_float<T>(gu[r * gu_stride + I + i]);
-    out[r * I + i] = from_float<T>(activation(g, act) * u);
+    out[r * I + i] = from_float<T>(activation(g, act) * u * rg);
   }
 }
 
@@ -138,25 +160,29 @@ KRK_API int krk_embed_scaled(float* out, const void* table, const int* ids, int 
 
 template <typename T>
 static int launch_rmsnorm_wide(void* out, float* x_new, const float* x, const void* branch, const float* gain,
-                               float offset, int rows, int H, float eps, cudaStream_t stream) {
+                               float offset, int rows, int H, float eps, const void* branch2, float bscale,
+                               const float* gain2, void* out2, cudaStream_t stream) {
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 220 * 1024) return -2;
   const int threads = H >= 4096 ? 1024 : (H >= 1024 ? 256 : 128);
-  const bool vec = H % 4 == 0 && ((uintptr_t)gain & 15) == 0;
+  const bool vec = H % 4 == 0 && ((uintptr_t)gain & 15) == 0 && ((uintptr_t)gain2 & 15) == 0;
   auto kern = vec ? rmsnorm_wide_kernel<T, true> : rmsnorm_wide_kernel<T, false>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   return (int)launch_pdl(kern, dim3(rows), dim3(threads), smem, stream, (T*)out, x_new, x, (const T*)branch, gain, offset,
-                         H, eps);
+                         H, eps, (const T*)branch2, bscale, gain2, (T*)out2);
 }
 
 KRK_API int krk_rmsnorm_wide(void* out, float* x_new, const float* x, const void* branch, const float* gain, float offset,
-                             int rows, int H, float eps, int dtype, cudaStream_t stream) {
+                             int rows, int H, float eps, const void* branch2, float bscale, const float* gain2, void* out2,
+                             int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
-  return dtype == KRK_DTYPE_F32 ? launch_rmsnorm_wide<float>(out, x_new, x, branch, gain, offset, rows, H, eps, stream)
-                                : launch_rmsnorm_wide<bf16>(out, x_new, x, branch, gain, offset, rows, H, eps, stream);
+  if (!branch && branch2) return -2;
+  return dtype == KRK_DTYPE_F32
+             ? launch_rmsnorm_wide<float>(out, x_new, x, branch, gain, offset, rows, H, eps, branch2, bscale, gain2, out2, stream)
+             : launch_rmsnorm_wide<bf16>(out, x_new, x, branch, gain, offset, rows, H, eps, branch2, bscale, gain2, out2, stream);
 }
 
-KRK_API int krk_gated_act(void* out, const void* gu, int gu_stride, int rows, int I, int act, int dtype,
+KRK_API int krk_gated_act(void* out, const void* gu, int gu_stride, int rows, int I, int act, int row_gate_col, int dtype,
                           cudaStream_t stream) {
   if (rows == 0) return 0;
   const size_t esz = dtype == KRK_DTYPE_F32 ? 4 : 2;
@@ -164,7 +190,7 @@ KRK_API int krk_gated_act(void* out, const void* gu, int gu_stride, int rows, in
   const int chunks = min(64, (I / (vec ? 4 : 1) + 255) / 256);
   if (dtype == KRK_DTYPE_F32)
     return (int)launch_pdl(vec ? gated_act_kernel<float, true> : gated_act_kernel<float, false>, dim3(rows, chunks),
-                           dim3(256), 0, stream, (float*)out, (const float*)gu, gu_stride, I, act);
+                           dim3(256), 0, stream, (float*)out, (const float*)gu, gu_stride, I, act, row_gate_col);
   return (int)launch_pdl(vec ? gated_act_kernel<bf16, true> : gated_act_kernel<bf16, false>, dim3(rows, chunks), dim3(256),
-                         0, stream, (bf16*)out, (const bf16*)gu, gu_stride, I, act);
+                         0, stream, (bf16*)out, (const bf16*)gu, gu_stride, I, act, row_gate_col);
 }

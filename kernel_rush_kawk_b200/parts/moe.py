@@ -59,7 +59,7 @@ class RoutedExperts(FeedForward):
 
     def bind(self, tensors, runtime):
         E = self.experts
-        self.router_w = tensors["router"].float().contiguous()
+        self.router_w = tensors["router"].contiguous()  # in the path's dtype: the logits' product accumulates in 32-bit
         self.router_b = tensors["router.b"].float().contiguous()
         self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0) for e in range(E)]).contiguous()
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(E)]).contiguous()
