@@ -26,6 +26,11 @@ delta rule, RWKV-style time mixing, a 32-bit residual stream) at two layer sizes
 equal width, feed-forward, head and layer counts: prefill of 2,048 tokens and decode at batch 1 and 8 after
 1,024-token prompts, each with the time per family of kernels, and prints a line of its own.
 
+``--only design_disorax`` does the same for the Disorax decoder (attention with a window that keeps the first
+tokens, attention over one cached low-rank row per token, routed experts with a shared one) at two sizes; its
+Qwen3 twin has the same width, head count and head size, and a feed-forward as wide as what one token runs
+through (chosen experts plus the shared one).
+
 ``--only workload_8b`` and ``--only workload_14b`` run the baseline's two larger
 configurations (Qwen3-8B sizes: 8 prompts of 256 to 2,048 tokens, 128 greedy steps;
 Qwen3-14B sizes: 16 prompts of 512 to 4,096 tokens, 128 steps at temperature 0.7)
@@ -192,24 +197,31 @@ def run_workload(args) -> dict:
 
 
 DESIGN_SIZES = {
-    # Taredra preset -> the Qwen3 decoder of equal width, feed-forward, heads and layers
+    # preset of a design -> the Qwen3 decoder of equal width, feed-forward, heads and layers
     "taredra_1b": {"hidden_size": 1536, "intermediate_size": 6144, "num_attention_heads": 12, "num_key_value_heads": 4,
                    "head_dim": 128, "vocab_size": 32768},
     "taredra_4b": {"hidden_size": 2560, "intermediate_size": 9728, "num_attention_heads": 32, "num_key_value_heads": 8,
                    "head_dim": 128, "vocab_size": 151936},
+    "disorax_small": {"hidden_size": 1024, "intermediate_size": 2048, "num_attention_heads": 8, "num_key_value_heads": 2,
+                      "head_dim": 128, "vocab_size": 32768},
+    "disorax_lite": {"hidden_size": 2048, "intermediate_size": 11264, "num_attention_heads": 16, "num_key_value_heads": 4,
+                     "head_dim": 128, "vocab_size": 32768},
 }
 KERNEL_FAMILIES = {
     "product": ("_skinny", "_library_gemm", "_gemm_nt", "gemm_tcgen05"),
     "norm": ("rmsnorm", "add_rmsnorm", "rmsnorm_wide"),
     "activation": ("swiglu", "gated_act"),
-    "attention": ("rope_attention", "rotate_norm_write", "sink_attention"),
+    "attention": ("rope_attention", "rotate_norm_write", "sink_attention", "latent_norm_write", "head_linear"),
     "recurrence": ("token_shift", "linear_recurrence"),
+    # routing and the routed experts; for steps of many tokens this holds the experts' dense products too, which
+    # the product family counts as well
+    "experts": ("moe_route", "moe_experts"),
     "embedding": ("embed", "embed_scaled", "gather_rows"),
 }
 
 
 def run_designs(args) -> dict:
-    """Taredra beside the Qwen3 decoder of equal size; see the module text."""
+    """A design (``--only design_<name>``) beside the Qwen3 decoder of equal size; see the module text."""
     import torch
 
     from kernel_rush_kawk_b200 import Engine, Qwen3Config, StepEntry
@@ -304,13 +316,16 @@ def run_designs(args) -> dict:
         torch.cuda.empty_cache()
         return res
 
+    design = args.only[len("design_"):]
     for preset, twin in DESIGN_SIZES.items():
+        if not preset.startswith(design + "_"):
+            continue
         t_cfg = preset_config(preset)
         layers = args.layers or len(t_cfg.layers)
         t_cfg = type(t_cfg).from_dict({**t_cfg.to_dict(), "layers": t_cfg.to_dict()["layers"][:layers]})
         q_cfg = Qwen3Config.from_dict({**twin, "num_hidden_layers": layers, "rms_norm_eps": 1e-6, "rope_theta": 1e4,
                                        "tie_word_embeddings": True, "max_position_embeddings": CONTEXT})
-        out["sizes"][preset] = {"layers": layers, "taredra": measure(t_cfg, t_cfg.vocab),
+        out["sizes"][preset] = {"layers": layers, design: measure(t_cfg, t_cfg.vocab),
                                 "qwen3": measure(q_cfg, q_cfg.vocab_size)}
     return out
 
@@ -621,7 +636,7 @@ def main() -> int:
     p.add_argument("--warmup", type=int, default=8)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--only", default="", choices=["", "prefill", "decode_b1", "decode_b8", "decode_b16", "decode_b32", "decode_b64",
-                                                  "workload_8b", "workload_14b", "design_taredra"],
+                                                  "workload_8b", "workload_14b", "design_taredra", "design_disorax"],
                    help="run one piece only (for profiling), or one of the baseline's larger configurations end to end")
     p.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (both numbers are reported)")
     args = p.parse_args()
@@ -633,7 +648,7 @@ def main() -> int:
         print(f"bench.py runs on one GPU only (this library has no multi-GPU path); got --gpus {args.gpus}")
         return 2
     args.warmup = max(args.warmup, 3)
-    if args.only == "design_taredra":
+    if args.only.startswith("design_"):
         print(json.dumps(run_designs(args)))
         return 0
     print(json.dumps(run_workload(args) if args.only in WORKLOADS else run_ours(args)))

@@ -319,6 +319,9 @@ attention_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ qkv, i
 // The same walk for windowed attention with a softmax sink: every row starts from (maximum = its head's
 // sink, sum = 1, no value) instead of (-inf, 0); the weights reach P.V as two bfloat16 halves; queries are
 // read from, and outputs written into, column ranges of wider rows, the output multiplied by out_scale.
+// Options: a windowed query also sees the first keep_first keys (their pages are walked before the window's,
+// and the cache may hold them for good in its first keep_pages table entries); the output is multiplied by
+// sigmoid(gate), one number per head (mode 1) or per element (mode 2) of the row's gate columns.
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(THREADS)
 sink_window_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_scale, const bf16* __restrict__ q_base,
@@ -326,7 +329,8 @@ sink_window_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_sca
                            const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                            const int* __restrict__ seq_qlen, const int* __restrict__ cu_q, const int* __restrict__ table,
                            int width, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-                           float scale_log2, int window) {
+                           float scale_log2, int window, int keep_first, int keep_pages,
+                           const bf16* __restrict__ gate, int gate_stride, int gate_mode) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* smem = reinterpret_cast<bf16*>(smem_raw);  // [2 stages][K, V][64][KVP]
   const int seq = blockIdx.z, kh = blockIdx.y;
@@ -341,6 +345,7 @@ sink_window_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_sca
 
   int pos[2], lo[2];
   const bf16* qp[2];
+  const bf16* gp[2];
   bf16* op[2];
   float m[2], l[2];
 #pragma unroll
@@ -353,6 +358,8 @@ sink_window_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_sca
     lo[h] = (ok && window > 0) ? max(0, pos[h] - window + 1) : 0;
     qp[h] = ok ? q_base + (size_t)(row0 + tok) * q_stride + (size_t)head * D : nullptr;
     op[h] = ok ? out + (size_t)(row0 + tok) * out_stride + (size_t)head * D : nullptr;
+    gp[h] = (ok && gate_mode) ? gate + (size_t)(row0 + tok) * gate_stride + (gate_mode == 2 ? (size_t)head * D : (size_t)head)
+                              : nullptr;
     m[h] = sink ? sink[head] * LOG2E : -INFINITY;
     l[h] = sink ? 1.f : 0.f;
   }
@@ -371,8 +378,16 @@ sink_window_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_sca
   const size_t page_stride = (size_t)HKV * KRK_PAGE * D;
   const size_t head_off = (size_t)kh * KRK_PAGE * D;
 
-  auto issue = [&](int j, int stage) {
-    const int page = table[(size_t)slot * width + j % width];
+  // pages of kept first keys that lie wholly before the window's first page are walked first: step i of the walk
+  // is page i while i < n_kept, page j_lo + (i - n_kept) after that
+  const int keep = window > 0 ? keep_first : 0;
+  const int n_kept = keep > 0 ? min((keep - 1) / KRK_PAGE + 1, j_lo) : 0;
+  const int n_steps = n_kept + (j_hi - j_lo + 1);
+  const int ring = max(width - keep_pages, 1);
+  auto page_index = [&](int i) { return i < n_kept ? i : j_lo + (i - n_kept); };
+  auto issue = [&](int i, int stage) {
+    const int j = page_index(i);
+    const int page = table[(size_t)slot * width + (j < keep_pages ? j : keep_pages + (j - keep_pages) % ring)];
     bf16* ks = smem + (size_t)stage * 2 * TILE_ELEMS;
     load_page(ks, k_cache + (size_t)page * page_stride + head_off);
     load_page(ks + TILE_ELEMS, v_cache + (size_t)page * page_stride + head_off);
@@ -385,11 +400,11 @@ sink_window_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_sca
 #pragma unroll
     for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
 
-  issue(j_lo, 0);
-  for (int j = j_lo; j <= j_hi; ++j) {
-    const int stage = (j - j_lo) & 1;
-    if (j + 1 <= j_hi) {
-      issue(j + 1, stage ^ 1);
+  issue(0, 0);
+  for (int i = 0; i < n_steps; ++i) {
+    const int stage = i & 1;
+    if (i + 1 < n_steps) {
+      issue(i + 1, stage ^ 1);
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
@@ -399,15 +414,15 @@ sink_window_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_sca
     const bf16* vs = ks + TILE_ELEMS;
     float s[8][4];
     qk_tile<8>(s, qf, ks, 0, lane);
-    const int key_base = j * KRK_PAGE;
-    const bool whole = key_base + KRK_PAGE - 1 <= warp_min_pos && key_base >= warp_max_lo;
+    const int key_base = page_index(i) * KRK_PAGE;
+    const bool whole = key_base + KRK_PAGE - 1 <= warp_min_pos && (key_base >= warp_max_lo || key_base + KRK_PAGE <= keep);
 #pragma unroll
     for (int n = 0; n < 8; ++n)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int key = key_base + n * 8 + 2 * t4 + (c & 1);
         const int h = c >> 1;
-        s[n][c] = (whole || (key <= pos[h] && key >= lo[h])) ? s[n][c] * scale_log2 : -INFINITY;
+        s[n][c] = (whole || (key <= pos[h] && (key >= lo[h] || key < keep))) ? s[n][c] * scale_log2 : -INFINITY;
       }
     softmax_update<8>(s, m, l, o);
     pv_tile_wide<8>(o, s, vs, 0, lane);
@@ -416,10 +431,17 @@ sink_window_prefill_kernel(bf16* __restrict__ out, int out_stride, float out_sca
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if (!op[h]) continue;
-    const float inv = out_scale / l[h];
+    float inv = out_scale / l[h];
+    if (gate_mode == 1) inv /= 1.0f + expf(-__bfloat162float(gp[h][0]));
 #pragma unroll
-    for (int n = 0; n < DTILES; ++n)
-      *reinterpret_cast<uint32_t*>(op[h] + n * 8 + 2 * t4) = pack_bf16x2(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+    for (int n = 0; n < DTILES; ++n) {
+      float a = o[n][2 * h] * inv, b = o[n][2 * h + 1] * inv;
+      if (gate_mode == 2) {
+        a /= 1.0f + expf(-__bfloat162float(gp[h][n * 8 + 2 * t4]));
+        b /= 1.0f + expf(-__bfloat162float(gp[h][n * 8 + 2 * t4 + 1]));
+      }
+      *reinterpret_cast<uint32_t*>(op[h] + n * 8 + 2 * t4) = pack_bf16x2(a, b);
+    }
   }
 }
 
@@ -1380,7 +1402,8 @@ KRK_API int krk_sink_window_prefill(void* out, int out_stride, float out_scale, 
                                     int HKV, const float* sink, const int* seq_slot, const int* seq_start,
                                     const int* seq_qlen, const int* cu_q, const int* table, int width,
                                     const void* k_cache, const void* v_cache, int n_seqs, int max_q_len, float scale,
-                                    int window, cudaStream_t stream) {
+                                    int window, int keep_first, int keep_pages, const void* gate, int gate_stride,
+                                    int gate_mode, cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return 0;
   const int G = HQ / HKV;
   const long long tiles = ((long long)max_q_len * G + 63) / 64;
@@ -1394,7 +1417,8 @@ KRK_API int krk_sink_window_prefill(void* out, int out_stride, float out_scale, 
   dim3 grid((unsigned)tiles, HKV, n_seqs);
   sink_window_prefill_kernel<<<grid, THREADS, PAGE_SMEM, stream>>>(
       (bf16*)out, out_stride, out_scale, (const bf16*)q_base, q_stride, HQ, HKV, sink, seq_slot, seq_start, seq_qlen,
-      cu_q, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale * LOG2E, window);
+      cu_q, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale * LOG2E, window, keep_first, keep_pages,
+      (const bf16*)gate, gate_stride, gate_mode);
   KRK_CHECK_LAUNCH();
   return 0;
 }

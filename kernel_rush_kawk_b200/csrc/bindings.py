@@ -69,8 +69,9 @@ _MOE_SIGNATURES = {
     "krk_moe_route": [_P, _P, _P, _P, c_int, c_int, c_int, _P],
     "krk_moe_gate_up_pairs": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_moe_down_pairs": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
-    "krk_moe_sort": [_P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P],
-    "krk_moe_combine": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
+    "krk_moe_sort": [_P, _P, _P, c_int, c_int, c_int, _P],
+    "krk_moe_gather": [_P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "krk_moe_combine": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, _P],
 }
 _SCAN_SIGNATURES = {
     "krk_token_shift": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P],
@@ -85,7 +86,7 @@ _ATTN_SIGNATURES = {
     "krk_attention_prefill": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_float,
                               c_int, _P],
     "krk_sink_window_prefill": [_P, c_int, c_float, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int,
-                                c_int, c_float, c_int, _P],
+                                c_int, c_float, c_int, c_int, c_int, _P, c_int, c_int, _P],
     "krk_attention_decode": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_float, c_int, c_int, _P,
                              _P],
     "krk_attention_prefill_tcgen05": [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int,
@@ -550,6 +551,16 @@ class Kernels:
         if out is None:
             out = torch.empty((x.shape[0], heads * N), dtype=x.dtype, device=x.device)
         optr, ostride = self._rows_view(out)
+        rows = x.shape[0]
+        if rows > self.SKINNY_MAX_ROWS and x.dtype == torch.bfloat16:
+            # many rows in bfloat16: the library's batched product, one batch entry per head
+            y = torch.bmm(x.view(rows, heads, K).transpose(0, 1), w.transpose(1, 2))  # [heads, rows, N]
+            dst = out[:, out_col:out_col + heads * N].view(rows, heads, N)
+            if out_scale == 1.0:
+                dst.copy_(y.transpose(0, 1))
+            else:
+                torch.mul(y.transpose(0, 1), out_scale, out=dst)
+            return out
         self._ok(self.mix.krk_head_linear(optr, ostride, int(out_col), float(out_scale), ptr, stride, w.data_ptr(), heads, N,
                                           K, x.shape[0], _code(x.dtype), self._stream()), "per-head product")
         return out
@@ -585,22 +596,38 @@ class Kernels:
                                                  experts.data_ptr(), weights.data_ptr(), rows, top, C, F, _code(x.dtype),
                                                  self._stream()), "experts' down")
             return out
-        # many rows: ordered by expert on the device; the experts' row ranges come to the host (a step of many
-        # tokens is never replayed from a graph), and each expert's rows go through the dense products
+        # many rows: ordered by expert on the device; the experts' row counts come to the host (a step of many
+        # tokens is never replayed from a graph)
         offsets = torch.empty(E + 1, dtype=torch.int32, device=x.device)
         place = torch.empty(rows * top, dtype=torch.int32, device=x.device)
-        xg = torch.empty((rows * top, K), dtype=x.dtype, device=x.device)
-        self._ok(self.moe.krk_moe_sort(offsets.data_ptr(), place.data_ptr(), xg.data_ptr(), ptr, stride, experts.data_ptr(),
-                                       rows, top, E, K, _code(x.dtype), self._stream()), "expert ordering")
+        self._ok(self.moe.krk_moe_sort(offsets.data_ptr(), place.data_ptr(), experts.data_ptr(), rows, top, E,
+                                       self._stream()), "expert ordering")
         bounds = offsets.tolist()
-        yg = torch.empty((rows * top, C), dtype=x.dtype, device=x.device)
-        for e in range(E):
-            a, b = bounds[e], bounds[e + 1]
-            if b > a:
-                h = self.gate_up_act(xg[a:b], w_gate_up[e], F, activation)
-                yg[a:b] = self.linear(h, w_down[e])
-        self._ok(self.moe.krk_moe_combine(out.data_ptr(), _ptr(add), yg.data_ptr(), place.data_ptr(), weights.data_ptr(),
-                                          rows, top, C, _code(x.dtype), self._stream()), "experts' sum")
+        most = max(bounds[e + 1] - bounds[e] for e in range(E))
+        cap = -(-most // 16) * 16
+        batched = x.dtype == torch.bfloat16 and E * cap <= 4 * rows * top
+        if not batched:
+            cap = 0
+        n_rows = E * cap if batched else rows * top
+        xg = torch.empty((n_rows, K), dtype=x.dtype, device=x.device)
+        self._ok(self.moe.krk_moe_gather(xg.data_ptr(), ptr, stride, place.data_ptr(), experts.data_ptr(), offsets.data_ptr(),
+                                         cap, rows, top, K, _code(x.dtype), self._stream()), "expert gather")
+        if batched:
+            # bfloat16: every expert's rows start at a multiple of cap (the most rows any expert got), and the
+            # library's batched product takes all experts at once; the rows beyond an expert's own are never read back
+            gu = torch.bmm(xg.view(E, cap, K), w_gate_up.transpose(1, 2))
+            h = self.gated_act(gu.view(E * cap, 2 * F), F, activation)
+            yg = torch.bmm(h.view(E, cap, F), w_down.transpose(1, 2)).view(E * cap, C)
+        else:
+            yg = torch.empty((n_rows, C), dtype=x.dtype, device=x.device)
+            for e in range(E):
+                a, b = bounds[e], bounds[e + 1]
+                if b > a:
+                    h = self.gate_up_act(xg[a:b], w_gate_up[e], F, activation)
+                    yg[a:b] = self.linear(h, w_down[e])
+        self._ok(self.moe.krk_moe_combine(out.data_ptr(), _ptr(add), yg.data_ptr(), place.data_ptr(), experts.data_ptr(),
+                                          offsets.data_ptr(), cap, weights.data_ptr(), rows, top, C, _code(x.dtype),
+                                          self._stream()), "experts' sum")
         return out
 
     def gate_up_act(self, h, w_gate_up, intermediate, activation):
@@ -657,7 +684,6 @@ class Kernels:
                 raise KernelError("the gate's rows have the queries' dtype and number")
             (g_ptr, g_stride), g_col, g_mode = self._rows_view(g_rows), int(gate[0]), {"head": 1, "element": 2}[gate[1]]
         extras = (keep_first, keep_pages, g_ptr, g_stride, g_col, g_mode)
-        plain = not (keep_first or keep_pages or g_mode)
         if batch.is_decode and proj.shape[0] == batch.n_seqs:
             # one token per sequence: a block per (sequence, kv head), its warps splitting the window's keys. The
             # choice depends on the step's shape alone, so a sequence's results do not depend on its batch
@@ -684,7 +710,7 @@ class Kernels:
                 return False
         elif fuse:
             return False
-        if (plain and proj.dtype == torch.bfloat16 and dim == vdim and dim % 16 == 0 and dim <= 256 and dim in self.attn
+        if (proj.dtype == torch.bfloat16 and dim == vdim and dim % 16 == 0 and dim <= 256 and dim in self.attn
                 and not batch.is_decode and hasattr(self.attn[dim], "krk_sink_window_prefill")):
             # many tokens per sequence in bfloat16: the tensor-core walk over whole pages (compiled per head size)
             esz = proj.element_size()
@@ -692,7 +718,8 @@ class Kernels:
                 optr + out_col * esz, ostride, float(out_scale), ptr + q_col * esz, stride, heads, cache.kv_heads,
                 _ptr(sink), batch.seq_slot.data_ptr(), batch.seq_start.data_ptr(), batch.seq_qlen.data_ptr(),
                 batch.cu_q.data_ptr(), cache.table.data_ptr(), cache.width, cache.k.data_ptr(), cache.v.data_ptr(),
-                batch.n_seqs, batch.max_q_len, float(scale), int(window or 0), self._stream())
+                batch.n_seqs, batch.max_q_len, float(scale), int(window or 0), keep_first, keep_pages,
+                None if g_ptr is None else g_ptr + g_col * esz, g_stride, g_mode, self._stream())
             if rc != -2:  # -2: odd strides or offsets; the general kernel takes them
                 self._ok(rc, "tensor-core windowed attention with a sink")
                 return

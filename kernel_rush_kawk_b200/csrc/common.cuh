@@ -142,6 +142,30 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return warp_sum(t);
 }
 
+// A lane's share of the dot product of a weight row (global memory) with a float32 vector (shared memory): lanes take
+// 16-byte pieces of a bfloat16 row in turn where the row allows it, single elements otherwise. The caller adds the
+// lanes' shares with warp_sum. The order of the sums depends on K alone.
+template <typename T> __device__ __forceinline__ float lane_dot(const T* __restrict__ w, const float* xs, int K, int lane) {
+  float acc = 0.f;
+  for (int k = lane; k < K; k += 32) acc += to_float<T>(w[k]) * xs[k];
+  return acc;
+}
+template <> __device__ __forceinline__ float lane_dot<bf16>(const bf16* __restrict__ w, const float* xs, int K, int lane) {
+  float acc = 0.f;
+  if ((K & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    for (int k = lane * 8; k < K; k += 256) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(w + k);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float4 a = *reinterpret_cast<const float4*>(xs + k), b = *reinterpret_cast<const float4*>(xs + k + 4);
+      acc += __low2float(p[0]) * a.x + __high2float(p[0]) * a.y + __low2float(p[1]) * a.z + __high2float(p[1]) * a.w +
+             __low2float(p[2]) * b.x + __high2float(p[2]) * b.y + __low2float(p[3]) * b.z + __high2float(p[3]) * b.w;
+    }
+    return acc;
+  }
+  for (int k = lane; k < K; k += 32) acc += __bfloat162float(w[k]) * xs[k];
+  return acc;
+}
+
 // Page of position `pos` for cache slot `slot`: table is [slots, width].
 __device__ __forceinline__ int page_of(const int* __restrict__ table, int width, int slot, int pos) {
   return table[(size_t)slot * width + (pos / KRK_PAGE) % width];

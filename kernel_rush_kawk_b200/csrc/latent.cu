@@ -42,7 +42,8 @@ template <typename T>
 __global__ void __launch_bounds__(HL_WARPS * 32)
 head_linear_kernel(T* __restrict__ out, int out_stride, int out_col, float out_scale, const T* __restrict__ x,
                    int x_stride, const T* __restrict__ w, int N, int K, int rows) {
-  extern __shared__ float xs[];  // [HL_ROWS][K]
+  extern __shared__ __align__(16) float xs[];  // [HL_ROWS][K4], K4 = K rounded up to a multiple of 4
+  const int K4 = (K + 3) & ~3;
   grid_launch_dependents();
   grid_dependency_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -50,23 +51,16 @@ head_linear_kernel(T* __restrict__ out, int out_stride, int out_col, float out_s
   const int nr = min(HL_ROWS, rows - r0);
   for (int i = threadIdx.x; i < HL_ROWS * K; i += blockDim.x) {
     const int r = i / K, k = i - r * K;
-    xs[i] = r < nr ? to_float<T>(x[(size_t)(r0 + r) * x_stride + (size_t)h * K + k]) : 0.f;
+    xs[r * K4 + k] = r < nr ? to_float<T>(x[(size_t)(r0 + r) * x_stride + (size_t)h * K + k]) : 0.f;
   }
   __syncthreads();
   for (int n = blockIdx.x * HL_WARPS + warp; n < N; n += gridDim.x * HL_WARPS) {
     const T* wr = w + ((size_t)h * N + n) * K;
-    float acc[HL_ROWS];
-#pragma unroll
-    for (int r = 0; r < HL_ROWS; ++r) acc[r] = 0.f;
-    for (int k = lane; k < K; k += 32) {
-      const float wv = to_float<T>(wr[k]);
-#pragma unroll
-      for (int r = 0; r < HL_ROWS; ++r) acc[r] += wv * xs[r * K + k];
-    }
     float mine = 0.f;
 #pragma unroll
     for (int r = 0; r < HL_ROWS; ++r) {
-      const float t = warp_sum(acc[r]);
+      if (r >= nr) break;
+      const float t = warp_sum(lane_dot<T>(wr, xs + r * K4, K, lane));  // the weight row comes from L1 after the first
       if (lane == r) mine = t;
     }
     if (lane < nr) out[(size_t)(r0 + lane) * out_stride + out_col + (size_t)h * N + n] = from_float<T>(mine * out_scale);
@@ -93,7 +87,7 @@ KRK_API int krk_latent_norm_write(const void* proj, int stride, int c_col, int R
 KRK_API int krk_head_linear(void* out, int out_stride, int out_col, float out_scale, const void* x, int x_stride,
                             const void* w, int heads, int N, int K, int rows, int dtype, cudaStream_t stream) {
   if (rows == 0 || heads == 0 || N == 0) return 0;
-  const size_t smem = (size_t)HL_ROWS * K * sizeof(float);
+  const size_t smem = (size_t)HL_ROWS * ((K + 3) & ~3) * sizeof(float);
   if (smem > 48 * 1024) return -2;
   const int row_tiles = (rows + HL_ROWS - 1) / HL_ROWS;
   if (heads > 65535 || row_tiles > 65535) return -3;

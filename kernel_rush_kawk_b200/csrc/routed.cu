@@ -8,9 +8,11 @@
 //   krk_moe_down_pairs: out[r, c] = add[r, c] + sum_j weight[r, j] * (Wd_e(j)[c] . act[(r, j)]), a warp per c;
 //   the sum over the chosen experts is float32, in the order of the choice.
 //
-// Many rows: pairs are counted per expert and ordered by expert on the device (krk_moe_sort: one block; offsets,
-// the pairs' places and the rows gathered in that order), the experts' products run over contiguous rows, and
-// krk_moe_combine adds each row's weighted results onto `add`.
+// Many rows: pairs are counted per expert and ordered by expert on the device (krk_moe_sort: one block; offsets
+// and the pairs' places), krk_moe_gather copies the rows into that order, the experts' products run over
+// contiguous rows, and krk_moe_combine adds each row's weighted results onto `add`. With cap > 0 every expert's
+// rows start at a multiple of cap (expert e's i-th pair sits in row e * cap + i), which is the layout a batched
+// product over [experts, cap, K] reads.
 #include "common.cuh"
 
 namespace {
@@ -68,7 +70,7 @@ template <typename T>
 __global__ void __launch_bounds__(PAIR_WARPS * 32)
 moe_gate_up_pairs_kernel(T* __restrict__ act_out, const T* __restrict__ x, int x_stride, const T* __restrict__ w,
                          const int* __restrict__ experts, int top, int F, int K, int act) {
-  extern __shared__ float xs[];  // [K]
+  extern __shared__ __align__(16) float xs[];  // [K]
   grid_launch_dependents();
   grid_dependency_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -81,14 +83,8 @@ moe_gate_up_pairs_kernel(T* __restrict__ act_out, const T* __restrict__ x, int x
   for (int f = blockIdx.x * PAIR_WARPS + warp; f < F; f += gridDim.x * PAIR_WARPS) {
     const T* wg = we + (size_t)f * K;
     const T* wu = we + (size_t)(F + f) * K;
-    float g = 0.f, u = 0.f;
-    for (int k = lane; k < K; k += 32) {
-      const float xv = xs[k];
-      g += to_float<T>(wg[k]) * xv;
-      u += to_float<T>(wu[k]) * xv;
-    }
-    g = warp_sum(g);
-    u = warp_sum(u);
+    const float g = warp_sum(lane_dot<T>(wg, xs, K, lane));
+    const float u = warp_sum(lane_dot<T>(wu, xs, K, lane));
     // the two products leave in the path's type before the activation, as they do from a product kernel
     if (lane == 0) act_out[(size_t)pair * F + f] = from_float<T>(act_of(round_to<T>(g), act) * round_to<T>(u));
   }
@@ -99,21 +95,20 @@ __global__ void __launch_bounds__(PAIR_WARPS * 32)
 moe_down_pairs_kernel(T* __restrict__ out, const T* __restrict__ add, const T* __restrict__ act_in,
                       const T* __restrict__ w, const int* __restrict__ experts, const float* __restrict__ weights, int top,
                       int C, int F) {
-  extern __shared__ float as[];  // [top][F]
+  extern __shared__ __align__(16) float as[];  // [top][F4], F4 = F rounded up to a multiple of 4
+  const int F4 = (F + 3) & ~3;
   grid_launch_dependents();
   grid_dependency_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = blockIdx.y;
-  for (int i = threadIdx.x; i < top * F; i += blockDim.x) as[i] = to_float<T>(act_in[(size_t)row * top * F + i]);
+  for (int i = threadIdx.x; i < top * F; i += blockDim.x) as[(i / F) * F4 + i % F] = to_float<T>(act_in[(size_t)row * top * F + i]);
   __syncthreads();
   for (int c = blockIdx.x * PAIR_WARPS + warp; c < C; c += gridDim.x * PAIR_WARPS) {
     float total = add ? to_float<T>(add[(size_t)row * C + c]) : 0.f;
     for (int j = 0; j < top; ++j) {
       const int e = experts[(size_t)row * top + j];
       const T* wr = w + ((size_t)e * C + c) * F;
-      float s = 0.f;
-      for (int k = lane; k < F; k += 32) s += to_float<T>(wr[k]) * as[j * F + k];
-      s = warp_sum(s);
+      const float s = warp_sum(lane_dot<T>(wr, as + j * F4, F, lane));
       total += weights[(size_t)row * top + j] * round_to<T>(s);
     }
     if (lane == 0) out[(size_t)row * C + c] = from_float<T>(total);
@@ -135,33 +130,59 @@ __global__ void moe_sort_kernel(int* __restrict__ offsets, int* __restrict__ pla
     for (int e = 0; e <= E; ++e) offsets[e] = cnt[e];
   }
   __syncthreads();
-  // a thread per expert walks the pairs in order: stable, and E is small beside the pairs' work that follows
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+  // a warp per expert walks the pairs in order, 32 at a time (a ballot gives each hit its rank): stable
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  for (int e = warp; e < E; e += n_warps) {
     int at = cnt[e];
-    for (int i = 0; i < pairs; ++i)
-      if (experts[i] == e) place[i] = at++;
+    for (int i0 = 0; i0 < pairs; i0 += 32) {
+      const int i = i0 + lane;
+      const bool hit = i < pairs && experts[i] == e;
+      const unsigned mask = __ballot_sync(0xffffffffu, hit);
+      if (hit) place[i] = at + __popc(mask & ((1u << lane) - 1u));
+      at += __popc(mask);
+    }
   }
+}
+
+__device__ __forceinline__ int row_of_pair(const int* __restrict__ place, const int* __restrict__ experts,
+                                           const int* __restrict__ offsets, int cap, int pair) {
+  if (cap <= 0) return place[pair];
+  const int e = experts[pair];
+  return e * cap + place[pair] - offsets[e];
 }
 
 template <typename T>
 __global__ void moe_gather_kernel(T* __restrict__ xg, const T* __restrict__ x, int x_stride, const int* __restrict__ place,
-                                  int top, int K) {
+                                  const int* __restrict__ experts, const int* __restrict__ offsets, int cap, int top, int K) {
   grid_dependency_wait();
   const int pair = blockIdx.x;
   const T* src = x + (size_t)(pair / top) * x_stride;
-  T* dst = xg + (size_t)place[pair] * K;
+  T* dst = xg + (size_t)row_of_pair(place, experts, offsets, cap, pair) * K;
+  if ((K * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    const int n = K * (int)sizeof(T) / 16;
+    for (int k = threadIdx.x; k < n; k += blockDim.x) reinterpret_cast<uint4*>(dst)[k] = reinterpret_cast<const uint4*>(src)[k];
+    return;
+  }
   for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = src[k];
 }
 
 template <typename T>
 __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ add, const T* __restrict__ yg,
-                                   const int* __restrict__ place, const float* __restrict__ weights, int top, int C) {
+                                   const int* __restrict__ place, const int* __restrict__ experts,
+                                   const int* __restrict__ offsets, int cap, const float* __restrict__ weights, int top,
+                                   int C) {
+  __shared__ int src_row[32];
+  __shared__ float src_w[32];
   grid_dependency_wait();
   const int row = blockIdx.x;
+  if (threadIdx.x < top) {
+    src_row[threadIdx.x] = row_of_pair(place, experts, offsets, cap, row * top + threadIdx.x);
+    src_w[threadIdx.x] = weights[(size_t)row * top + threadIdx.x];
+  }
+  __syncthreads();
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     float total = add ? to_float<T>(add[(size_t)row * C + c]) : 0.f;
-    for (int j = 0; j < top; ++j)
-      total += weights[(size_t)row * top + j] * to_float<T>(yg[(size_t)place[(size_t)row * top + j] * C + c]);
+    for (int j = 0; j < top; ++j) total += src_w[j] * to_float<T>(yg[(size_t)src_row[j] * C + c]);
     out[(size_t)row * C + c] = from_float<T>(total);
   }
 }
@@ -194,7 +215,7 @@ KRK_API int krk_moe_gate_up_pairs(void* act_out, const void* x, int x_stride, co
 KRK_API int krk_moe_down_pairs(void* out, const void* add, const void* act_in, const void* w, const int* experts,
                                const float* weights, int rows, int top, int C, int F, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
-  const size_t smem = (size_t)top * F * sizeof(float);
+  const size_t smem = (size_t)top * ((F + 3) & ~3) * sizeof(float);
   if (smem > 48 * 1024 || rows > 65535) return -2;
   const dim3 grid((unsigned)min((C + PAIR_WARPS - 1) / PAIR_WARPS, 1024), (unsigned)rows);
   if (dtype == KRK_DTYPE_F32)
@@ -204,26 +225,31 @@ KRK_API int krk_moe_down_pairs(void* out, const void* add, const void* act_in, c
                          (const bf16*)add, (const bf16*)act_in, (const bf16*)w, experts, weights, top, C, F);
 }
 
-KRK_API int krk_moe_sort(int* offsets, int* place, void* xg, const void* x, int x_stride, const int* experts, int rows,
-                         int top, int E, int K, int dtype, cudaStream_t stream) {
+KRK_API int krk_moe_sort(int* offsets, int* place, const int* experts, int rows, int top, int E, cudaStream_t stream) {
   if (rows == 0) return 0;
-  const int pairs = rows * top;
-  cudaError_t e = launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(E + 1) * sizeof(int), stream, offsets, place,
-                             experts, pairs, E);
-  if (e != cudaSuccess) return (int)e;
-  if (dtype == KRK_DTYPE_F32)
-    return (int)launch_pdl(moe_gather_kernel<float>, dim3(pairs), dim3(128), 0, stream, (float*)xg, (const float*)x,
-                           x_stride, (const int*)place, top, K);
-  return (int)launch_pdl(moe_gather_kernel<bf16>, dim3(pairs), dim3(128), 0, stream, (bf16*)xg, (const bf16*)x, x_stride,
-                         (const int*)place, top, K);
+  return (int)launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(E + 1) * sizeof(int), stream, offsets, place,
+                         experts, rows * top, E);
 }
 
-KRK_API int krk_moe_combine(void* out, const void* add, const void* yg, const int* place, const float* weights, int rows,
-                            int top, int C, int dtype, cudaStream_t stream) {
+KRK_API int krk_moe_gather(void* xg, const void* x, int x_stride, const int* place, const int* experts, const int* offsets,
+                           int cap, int rows, int top, int K, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
+  const int pairs = rows * top;
+  if (dtype == KRK_DTYPE_F32)
+    return (int)launch_pdl(moe_gather_kernel<float>, dim3(pairs), dim3(128), 0, stream, (float*)xg, (const float*)x,
+                           x_stride, place, experts, offsets, cap, top, K);
+  return (int)launch_pdl(moe_gather_kernel<bf16>, dim3(pairs), dim3(128), 0, stream, (bf16*)xg, (const bf16*)x, x_stride,
+                         place, experts, offsets, cap, top, K);
+}
+
+KRK_API int krk_moe_combine(void* out, const void* add, const void* yg, const int* place, const int* experts,
+                            const int* offsets, int cap, const float* weights, int rows, int top, int C, int dtype,
+                            cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (top > 32) return -2;
   if (dtype == KRK_DTYPE_F32)
     return (int)launch_pdl(moe_combine_kernel<float>, dim3(rows), dim3(256), 0, stream, (float*)out, (const float*)add,
-                           (const float*)yg, place, weights, top, C);
+                           (const float*)yg, place, experts, offsets, cap, weights, top, C);
   return (int)launch_pdl(moe_combine_kernel<bf16>, dim3(rows), dim3(256), 0, stream, (bf16*)out, (const bf16*)add,
-                         (const bf16*)yg, place, weights, top, C);
+                         (const bf16*)yg, place, experts, offsets, cap, weights, top, C);
 }

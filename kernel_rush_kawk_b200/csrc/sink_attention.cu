@@ -32,7 +32,8 @@
 
 namespace {
 
-constexpr int MAX_V_PER_LANE = 8;
+constexpr int MAX_V_PER_LANE = 8;    // value heads up to 256
+constexpr int WIDE_V_PER_LANE = 16;  // the general kernel's second form: value rows up to 512 (latent rows)
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }  // value heads up to 256
 
@@ -135,7 +136,7 @@ template <> __device__ __forceinline__ float dot_row<bf16>(const float* q, const
   return dot;
 }
 
-template <typename T>
+template <typename T, int VPL>
 __global__ void sink_attention_kernel(T* __restrict__ out, int out_stride, int out_col, float out_scale,
                                       const T* __restrict__ proj, int stride, int q_col, int HQ, int HKV, int D, int DV,
                                       const float* __restrict__ sink, const int* __restrict__ row_seq,
@@ -163,9 +164,9 @@ __global__ void sink_attention_kernel(T* __restrict__ out, int out_stride, int o
 
   float m = sink ? sink[head] : -INFINITY;
   float l = sink ? 1.f : 0.f;
-  float acc[MAX_V_PER_LANE];
+  float acc[VPL];
 #pragma unroll
-  for (int i = 0; i < MAX_V_PER_LANE; ++i) acc[i] = 0.f;
+  for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
 
   // the kept first keys that the window no longer covers, then the window's own
   const int kept_hi = (window > 0 && keep_first > 0) ? min(keep_first, first) - 1 : -1;
@@ -184,7 +185,7 @@ __global__ void sink_attention_kernel(T* __restrict__ out, int out_stride, int o
     const float p = key <= hi ? expf(s - m_new) : 0.f;
     l = l * alpha + warp_sum(p);
 #pragma unroll
-    for (int i = 0; i < MAX_V_PER_LANE; ++i) acc[i] *= alpha;
+    for (int i = 0; i < VPL; ++i) acc[i] *= alpha;
     const int n = min(32, hi - base + 1);
 #pragma unroll 4
     for (int j = 0; j < n; ++j) {
@@ -193,7 +194,7 @@ __global__ void sink_attention_kernel(T* __restrict__ out, int out_stride, int o
       const int page = __shfl_sync(0xffffffffu, my_page, j);  // lane j looked its key's page up already
       const T* vp = v_cache + (((size_t)page * HKV + kh) * KRK_PAGE + (kj % KRK_PAGE)) * DV;
 #pragma unroll
-      for (int i = 0; i < MAX_V_PER_LANE; ++i) {
+      for (int i = 0; i < VPL; ++i) {
         const int d = lane + 32 * i;
         if (d < DV) acc[i] += pj * to_float<T>(vp[d]);
       }
@@ -206,7 +207,7 @@ __global__ void sink_attention_kernel(T* __restrict__ out, int out_stride, int o
   const T* gp = gate_mode ? gate + (size_t)row * gate_stride + gate_col : nullptr;
   if (gate_mode == 1) inv *= sigmoidf_(to_float<T>(gp[head]));
 #pragma unroll
-  for (int i = 0; i < MAX_V_PER_LANE; ++i) {
+  for (int i = 0; i < VPL; ++i) {
     const int d = lane + 32 * i;
     if (d < DV) o[d] = from_float<T>(acc[i] * inv * (gate_mode == 2 ? sigmoidf_(to_float<T>(gp[(size_t)head * DV + d])) : 1.f));
   }
@@ -241,8 +242,10 @@ template <> __device__ __forceinline__ void load4<bf16>(const bf16* p, float* f,
   f[0] = __low2float(h[0]); f[1] = __high2float(h[0]); f[2] = __low2float(h[1]); f[3] = __high2float(h[1]);
 }
 
-// V4: value heads of a multiple of 4 elements up to 128, lane l holding elements 4l .. 4l + 3 of a row
-template <typename T, bool V4, bool FUSE>
+// V4: value heads of a multiple of 4 elements, lane l holding elements 4l .. 4l + 3 of every 128 of a row.
+// NV: a lane's elements of a value row (4: rows up to 128; 16: up to 512, with GM = 4 query heads a block so that
+// the accumulators stay in registers and the warps' shares in shared memory; four value rows in flight instead of 16)
+template <typename T, bool V4, bool FUSE, int NV, int GM>
 __global__ void __launch_bounds__(SINGLE_WARPS * 32)
 sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, float out_scale,
                              const T* __restrict__ proj, int stride, int q_col, int HQ, int HKV, int D, int DV,
@@ -320,14 +323,14 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
     }
   }
 
-  float m[GROUP_MAX], l[GROUP_MAX], acc[GROUP_MAX][MAX_V_PER_LANE / 2];
+  float m[GM], l[GM], acc[GM][NV];
 #pragma unroll
-  for (int g = 0; g < GROUP_MAX; ++g) {
+  for (int g = 0; g < GM; ++g) {
     const bool has = warp == 0 && split == 0 && sink != nullptr && g < GN;
     m[g] = has ? sink[head0 + g] : -INFINITY;
     l[g] = has ? 1.f : 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) acc[g][i] = 0.f;
+    for (int i = 0; i < NV; ++i) acc[g][i] = 0.f;
   }
   const bool vec = (D & 7) == 0;  // rows of the cache then start on 16-byte boundaries (32 for float)
   // the kept first keys that the window no longer covers, then the window's own; chunks of either go round the
@@ -337,9 +340,9 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
   const int lo = seg ? first : 0, hi = seg ? pos : kept_hi;
   for (int base = lo + 32 * (split + SPL * warp); base <= hi; base += 32 * SPL * SINGLE_WARPS) {
     const int key = base + lane;
-    float s[GROUP_MAX];
+    float s[GM];
 #pragma unroll
-    for (int g = 0; g < GROUP_MAX; ++g) s[g] = 0.f;
+    for (int g = 0; g < GM; ++g) s[g] = 0.f;
     int my_page = 0;
     if (key <= hi) {
       my_page = page_of(table, width, slot, key, keep_pages);
@@ -356,7 +359,7 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
 #pragma unroll
           for (int c = 0; c < 8; ++c)
 #pragma unroll
-            for (int g = 0; g < GROUP_MAX; ++g)
+            for (int g = 0; g < GM; ++g)
               if (g < GN) {
                 const float4 qa = *reinterpret_cast<const float4*>(q_s + g * D + d + 8 * c);
                 const float4 qb = *reinterpret_cast<const float4*>(q_s + g * D + d + 8 * c + 4);
@@ -368,7 +371,7 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
           float kf[8];
           load8<T>(kp + d, kf);
 #pragma unroll
-          for (int g = 0; g < GROUP_MAX; ++g)
+          for (int g = 0; g < GM; ++g)
             if (g < GN) {
               const float4 qa = *reinterpret_cast<const float4*>(q_s + g * D + d);
               const float4 qb = *reinterpret_cast<const float4*>(q_s + g * D + d + 4);
@@ -380,14 +383,14 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
         for (int d = 0; d < D; ++d) {
           const float kf = to_float<T>(kp[d]);
 #pragma unroll
-          for (int g = 0; g < GROUP_MAX; ++g)
+          for (int g = 0; g < GM; ++g)
             if (g < GN) s[g] += q_s[g * D + d] * kf;
         }
       }
     }
-    float p[GROUP_MAX];
+    float p[GM];
 #pragma unroll
-    for (int g = 0; g < GROUP_MAX; ++g) {
+    for (int g = 0; g < GM; ++g) {
       if (g >= GN) continue;
       const float sc = key <= hi ? s[g] * scale : -INFINITY;
       const float m_new = fmaxf(m[g], warp_max(sc));
@@ -395,36 +398,39 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
       p[g] = key <= hi ? expf(sc - m_new) : 0.f;
       l[g] = l[g] * alpha + warp_sum(p[g]);
 #pragma unroll
-      for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) acc[g][i] *= alpha;
+      for (int i = 0; i < NV; ++i) acc[g][i] *= alpha;
       m[g] = m_new;
     }
     const int n = min(32, hi - base + 1);
-    for (int j0 = 0; j0 < n; j0 += 16) {  // sixteen value rows are requested before the first is used
-      float vf[16][MAX_V_PER_LANE / 2];
+    constexpr int VR = NV == 4 ? 16 : 4;
+    for (int j0 = 0; j0 < n; j0 += VR) {  // VR value rows are requested before the first is used
+      float vf[VR][NV];
 #pragma unroll
-      for (int jj = 0; jj < 16; ++jj) {
+      for (int jj = 0; jj < VR; ++jj) {
         const int j = j0 + jj;
         const int kj = base + j;
         const int page = __shfl_sync(0xffffffffu, my_page, j & 31);  // lane j looked its key's page up already
         const T* vp = (FUSE && kj == pos) ? vn : v_cache + (((size_t)page * HKV + kh) * KRK_PAGE + (kj % KRK_PAGE)) * DV;
         if (V4) {  // four neighbouring elements per lane, one load
-          load4<T>(vp + 4 * lane, vf[jj], j < n && 4 * lane < DV);
+#pragma unroll
+          for (int cb = 0; cb < NV / 4; ++cb)
+            load4<T>(vp + 128 * cb + 4 * lane, vf[jj] + 4 * cb, j < n && 128 * cb + 4 * lane < DV);
         } else {
 #pragma unroll
-          for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) {
+          for (int i = 0; i < NV; ++i) {
             const int d = lane + 32 * i;
             vf[jj][i] = (j < n && d < DV) ? to_float<T>(vp[d]) : 0.f;
           }
         }
       }
 #pragma unroll
-      for (int jj = 0; jj < 16; ++jj)
+      for (int jj = 0; jj < VR; ++jj)
 #pragma unroll
-        for (int g = 0; g < GROUP_MAX; ++g) {
+        for (int g = 0; g < GM; ++g) {
           if (g >= GN) continue;
           const float pj = __shfl_sync(0xffffffffu, p[g], (j0 + jj) & 31);  // zero beyond the last key
 #pragma unroll
-          for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) acc[g][i] += pj * vf[jj][i];
+          for (int i = 0; i < NV; ++i) acc[g][i] += pj * vf[jj][i];
         }
     }
   }
@@ -432,13 +438,13 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
   // the warps' partial results, then one warp per head merges them in warp order
   const int PS = DV + 2;
 #pragma unroll
-  for (int g = 0; g < GROUP_MAX; ++g) {
+  for (int g = 0; g < GM; ++g) {
     if (g >= GN) continue;
     float* dst = part + ((size_t)warp * GN + g) * PS;
     if (lane == 0) { dst[DV] = m[g]; dst[DV + 1] = l[g]; }
 #pragma unroll
-    for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) {
-      const int d = V4 ? 4 * lane + i : lane + 32 * i;
+    for (int i = 0; i < NV; ++i) {
+      const int d = V4 ? (i >> 2) * 128 + 4 * lane + (i & 3) : lane + 32 * i;
       if (d < DV) dst[d] = acc[g][i];
     }
   }
@@ -446,16 +452,16 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
   for (int g = warp; g < GN; g += SINGLE_WARPS) {
     float mx = -INFINITY;
     for (int w = 0; w < SINGLE_WARPS; ++w) mx = fmaxf(mx, part[((size_t)w * GN + g) * PS + DV]);
-    float total = 0.f, o[MAX_V_PER_LANE / 2];
+    float total = 0.f, o[NV];
 #pragma unroll
-    for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) o[i] = 0.f;
+    for (int i = 0; i < NV; ++i) o[i] = 0.f;
     for (int w = 0; w < SINGLE_WARPS; ++w) {
       const float* src = part + ((size_t)w * GN + g) * PS;
       const float f = src[DV] == -INFINITY ? 0.f : expf(src[DV] - mx);
       total += src[DV + 1] * f;
 #pragma unroll
-      for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) {
-        const int d = V4 ? 4 * lane + i : lane + 32 * i;
+      for (int i = 0; i < NV; ++i) {
+        const int d = V4 ? (i >> 2) * 128 + 4 * lane + (i & 3) : lane + 32 * i;
         if (d < DV) o[i] += src[d] * f;
       }
     }
@@ -463,8 +469,8 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
       float* dst = scratch + (((size_t)item * SPL + split) * G + g0 + g) * PS;
       if (lane == 0) { dst[DV] = mx; dst[DV + 1] = total; }
 #pragma unroll
-      for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) {
-        const int d = V4 ? 4 * lane + i : lane + 32 * i;
+      for (int i = 0; i < NV; ++i) {
+        const int d = V4 ? (i >> 2) * 128 + 4 * lane + (i & 3) : lane + 32 * i;
         if (d < DV) dst[d] = o[i];
       }
       continue;
@@ -474,8 +480,8 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
     const T* gp = gate_mode ? gate + (size_t)seq * gate_stride + gate_col : nullptr;
     if (gate_mode == 1) inv *= sigmoidf_(to_float<T>(gp[head0 + g]));
 #pragma unroll
-    for (int i = 0; i < MAX_V_PER_LANE / 2; ++i) {
-      const int d = V4 ? 4 * lane + i : lane + 32 * i;
+    for (int i = 0; i < NV; ++i) {
+      const int d = V4 ? (i >> 2) * 128 + 4 * lane + (i & 3) : lane + 32 * i;
       if (d < DV)
         op[d] = from_float<T>(o[i] * inv * (gate_mode == 2 ? sigmoidf_(to_float<T>(gp[(size_t)(head0 + g) * DV + d])) : 1.f));
     }
@@ -498,28 +504,22 @@ __global__ void sink_attention_merge_kernel(T* __restrict__ out, int out_stride,
   const int seq = item / HKV, kh = item % HKV;
   float mx = -INFINITY;
   for (int sp = 0; sp < SPL; ++sp) mx = fmaxf(mx, scratch[(((size_t)item * SPL + sp) * G + g) * PS + DV]);
-  float total = 0.f, o[MAX_V_PER_LANE];
-#pragma unroll
-  for (int i = 0; i < MAX_V_PER_LANE; ++i) o[i] = 0.f;
+  float total = 0.f;
   for (int sp = 0; sp < SPL; ++sp) {
     const float* src = scratch + (((size_t)item * SPL + sp) * G + g) * PS;
-    const float f = src[DV] == -INFINITY ? 0.f : expf(src[DV] - mx);
-    total += src[DV + 1] * f;
-#pragma unroll
-    for (int i = 0; i < MAX_V_PER_LANE; ++i) {
-      const int d = lane + 32 * i;
-      if (d < DV) o[i] += src[d] * f;
-    }
+    total += src[DV] == -INFINITY ? 0.f : src[DV + 1] * expf(src[DV] - mx);
   }
   T* op = out + (size_t)seq * out_stride + out_col + (size_t)(kh * G + g) * DV;
   float inv = out_scale / total;
   const T* gp = gate_mode ? gate + (size_t)seq * gate_stride + gate_col : nullptr;
   if (gate_mode == 1) inv *= sigmoidf_(to_float<T>(gp[kh * G + g]));
-#pragma unroll
-  for (int i = 0; i < MAX_V_PER_LANE; ++i) {
-    const int d = lane + 32 * i;
-    if (d < DV)
-      op[d] = from_float<T>(o[i] * inv * (gate_mode == 2 ? sigmoidf_(to_float<T>(gp[(size_t)(kh * G + g) * DV + d])) : 1.f));
+  for (int d = lane; d < DV; d += 32) {  // value rows of any width; the shares are added in block order
+    float o = 0.f;
+    for (int sp = 0; sp < SPL; ++sp) {
+      const float* src = scratch + (((size_t)item * SPL + sp) * G + g) * PS;
+      if (src[DV] != -INFINITY) o += src[d] * expf(src[DV] - mx);
+    }
+    op[d] = from_float<T>(o * inv * (gate_mode == 2 ? sigmoidf_(to_float<T>(gp[(size_t)(kh * G + g) * DV + d])) : 1.f));
   }
 }
 
@@ -554,24 +554,26 @@ KRK_API int krk_sink_attention(void* out, int out_stride, int out_col, float out
                                const void* gate, int gate_stride, int gate_col, int gate_mode, int dtype,
                                cudaStream_t stream) {
   if (rows == 0) return 0;
-  if (DV > 32 * MAX_V_PER_LANE || D > 2048) return -2;
+  if (DV > 32 * WIDE_V_PER_LANE || D > 2048) return -2;
   const long long items = (long long)rows * HQ;
   const int warps = 4;
   const long long blocks = (items + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return -3;
   const size_t smem = (size_t)warps * D * sizeof(float);
+  const bool wide = DV > 32 * MAX_V_PER_LANE;
   if (dtype == KRK_DTYPE_F32)
-    return (int)launch_pdl(sink_attention_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream,
+    return (int)launch_pdl(wide ? sink_attention_kernel<float, WIDE_V_PER_LANE> : sink_attention_kernel<float, MAX_V_PER_LANE>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream,
                            (float*)out, out_stride, out_col, out_scale, (const float*)proj, stride, q_col, HQ, HKV, D, DV,
                            sink, row_seq, row_pos, seq_slot, table, width, (const float*)k_cache, (const float*)v_cache,
                            rows, scale, window, keep_first, keep_pages, (const float*)gate, gate_stride, gate_col, gate_mode);
-  return (int)launch_pdl(sink_attention_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, (bf16*)out,
+  return (int)launch_pdl(wide ? sink_attention_kernel<bf16, WIDE_V_PER_LANE> : sink_attention_kernel<bf16, MAX_V_PER_LANE>,
+                         dim3((unsigned)blocks), dim3(warps * 32), smem, stream, (bf16*)out,
                          out_stride, out_col, out_scale, (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink, row_seq,
                          row_pos, seq_slot, table, width, (const bf16*)k_cache, (const bf16*)v_cache, rows, scale, window,
                          keep_first, keep_pages, (const bf16*)gate, gate_stride, gate_col, gate_mode);
 }
 
-// One token per sequence: rows are the sequences, in order. Value heads of up to 128 elements; others take
+// One token per sequence: rows are the sequences, in order. Value heads of up to 512 elements; others take
 // krk_sink_attention. splits > 1: that many blocks share an item's keys and a merge kernel follows; scratch then
 // holds n_seqs * HQ * splits * (DV + 2) floats. fuse: the kernel also does what krk_rotate_norm_write does for the
 // step's rows (queries rotated on the way in, the new key and value made in shared memory and written to their page
@@ -584,46 +586,42 @@ KRK_API int krk_sink_attention_single(void* out, int out_stride, int out_col, fl
                                       int value_norm, float eps, int keep_first, int keep_pages, const void* gate,
                                       int gate_stride, int gate_col, int gate_mode, int dtype, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
-  if (DV > 32 * (MAX_V_PER_LANE / 2) || D > 1024) return -2;
+  if (DV > 512 || D > 1024) return -2;
   const int G = HQ / HKV;
   const int SPL = (splits > 1 && scratch) ? splits : 1;
-  if (fuse && G > GROUP_MAX) return -2;  // the new key and value are made by one launch per item
+  const bool wide = DV > 32 * (MAX_V_PER_LANE / 2);  // value rows beyond 128 elements: fewer heads a block
+  const int gm = wide ? 4 : GROUP_MAX;
+  if (fuse && (wide || G > GROUP_MAX)) return -2;  // the new key and value are made by one launch per item
   if (fuse && (rot < 0 || rot > D || (rot & 1))) return -2;
-  for (int g0 = 0; g0 < G; g0 += GROUP_MAX) {
-    const int GN = min(GROUP_MAX, G - g0);
+  for (int g0 = 0; g0 < G; g0 += gm) {
+    const int GN = min(gm, G - g0);
     const size_t esz = dtype == KRK_DTYPE_F32 ? 4 : 2;
     const size_t smem = ((size_t)GN * D + (size_t)SINGLE_WARPS * GN * (DV + 2) + 4) * sizeof(float) +
                         (((size_t)D + 7) / 8 * 8 + DV + 8) * esz;
     if (smem > 96 * 1024) return -2;
     cudaError_t e;
     const bool v4 = (DV & 3) == 0;  // rows of the value cache then start on 8-byte (16 for float) boundaries
-    if (smem > 48 * 1024) {
-      const int big = 100 * 1024;
-      cudaFuncSetAttribute(sink_attention_single_kernel<float, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-      cudaFuncSetAttribute(sink_attention_single_kernel<float, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-      cudaFuncSetAttribute(sink_attention_single_kernel<bf16, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-      cudaFuncSetAttribute(sink_attention_single_kernel<bf16, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-      cudaFuncSetAttribute(sink_attention_single_kernel<float, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-      cudaFuncSetAttribute(sink_attention_single_kernel<float, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-      cudaFuncSetAttribute(sink_attention_single_kernel<bf16, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-      cudaFuncSetAttribute(sink_attention_single_kernel<bf16, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-    }
-    if (dtype == KRK_DTYPE_F32)
-      e = launch_pdl(fuse ? (v4 ? sink_attention_single_kernel<float, true, true> : sink_attention_single_kernel<float, false, true>)
-                          : (v4 ? sink_attention_single_kernel<float, true, false> : sink_attention_single_kernel<float, false, false>),
-                     dim3(n_seqs * HKV * SPL), dim3(SINGLE_WARPS * 32), smem, stream,
+    if (dtype == KRK_DTYPE_F32) {
+      auto kern = wide ? (v4 ? sink_attention_single_kernel<float, true, false, 16, 4> : sink_attention_single_kernel<float, false, false, 16, 4>)
+                  : fuse ? (v4 ? sink_attention_single_kernel<float, true, true, 4, GROUP_MAX> : sink_attention_single_kernel<float, false, true, 4, GROUP_MAX>)
+                         : (v4 ? sink_attention_single_kernel<float, true, false, 4, GROUP_MAX> : sink_attention_single_kernel<float, false, false, 4, GROUP_MAX>);
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+      e = launch_pdl(kern, dim3(n_seqs * HKV * SPL), dim3(SINGLE_WARPS * 32), smem, stream,
                      (float*)out, out_stride, out_col, out_scale, (const float*)proj, stride, q_col, HQ, HKV, D, DV, sink,
                      seq_slot, seq_start, table, width, (const float*)k_cache, (const float*)v_cache, scale, window, g0, GN, SPL, scratch, k_col, v_col,
                      inv_freq, rot, value_norm, eps, (float*)k_cache, (float*)v_cache, keep_first, keep_pages,
                      (const float*)gate, gate_stride, gate_col, gate_mode);
-    else
-      e = launch_pdl(fuse ? (v4 ? sink_attention_single_kernel<bf16, true, true> : sink_attention_single_kernel<bf16, false, true>)
-                          : (v4 ? sink_attention_single_kernel<bf16, true, false> : sink_attention_single_kernel<bf16, false, false>),
-                     dim3(n_seqs * HKV * SPL), dim3(SINGLE_WARPS * 32), smem, stream,
+    } else {
+      auto kern = wide ? (v4 ? sink_attention_single_kernel<bf16, true, false, 16, 4> : sink_attention_single_kernel<bf16, false, false, 16, 4>)
+                  : fuse ? (v4 ? sink_attention_single_kernel<bf16, true, true, 4, GROUP_MAX> : sink_attention_single_kernel<bf16, false, true, 4, GROUP_MAX>)
+                         : (v4 ? sink_attention_single_kernel<bf16, true, false, 4, GROUP_MAX> : sink_attention_single_kernel<bf16, false, false, 4, GROUP_MAX>);
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+      e = launch_pdl(kern, dim3(n_seqs * HKV * SPL), dim3(SINGLE_WARPS * 32), smem, stream,
                      (bf16*)out, out_stride, out_col, out_scale, (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink,
                      seq_slot, seq_start, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale, window, g0, GN, SPL, scratch, k_col, v_col,
                      inv_freq, rot, value_norm, eps, (bf16*)k_cache, (bf16*)v_cache, keep_first, keep_pages,
                      (const bf16*)gate, gate_stride, gate_col, gate_mode);
+    }
     if (e != cudaSuccess) return (int)e;
   }
   if (SPL > 1) {

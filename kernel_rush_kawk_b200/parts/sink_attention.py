@@ -85,7 +85,7 @@ class SinkWindowAttention(Branch):
     def attention_head_dims(self):
         """Steps of many tokens in bfloat16 run on the tensor cores where key and value heads have one size that
         is a multiple of 16: that kernel is compiled per head size."""
-        return (self.dim,) if self._plain and self.dim == self.vdim and self.dim % 16 == 0 and self.dim <= 256 else ()
+        return (self.dim,) if self.dim == self.vdim and self.dim % 16 == 0 and self.dim <= 256 else ()
 
     def bind(self, tensors, runtime):
         self.w = {k: tensors[k] for k in ("q", "k", "v", "o") + (("g",) if self.gate else ())}

@@ -30,7 +30,9 @@ def runtime(dtype):
     from kernel_rush_kawk_b200.csrc import load_kernels
     from kernel_rush_kawk_b200.engine.model import Runtime
 
-    return Runtime(torch.device("cuda:0"), dtype, load_kernels(()))
+    # with the per-head-size attention libraries of these sizes loaded, bfloat16 steps of many tokens whose key and
+    # value heads have one of them take the tensor-core kernel; all others the general one
+    return Runtime(torch.device("cuda:0"), dtype, load_kernels((16, 32)))
 
 
 def rand(shape, seed, scale=1.0):
@@ -120,6 +122,8 @@ ATTN_SHAPES = [  # hidden, heads, kv_heads, dim, vdim, window, keep_first, rot, 
     (48, 3, 1, 8, 40, 130, 64, 2, 10.0, None, True),
     (50, 3, 3, 6, 5, 3, 2, 4, 7.0, "element", True),
     (40, 10, 1, 8, 8, 90, 0, 4, 30.0, "element", False),
+    (64, 4, 2, 32, 32, 70, 66, 8, 2e4, "head", True),   # kept tokens over two pages, walked before the window's pages
+    (48, 4, 1, 16, 16, 200, 130, 16, 1e4, "element", False),
 ]
 
 
@@ -211,6 +215,8 @@ LATENT_SHAPES = [  # hidden, heads, dim, vdim, rank, window, sink
     (48, 1, 64, 16, 8, None, False),
     (64, 12, 8, 8, 96, 70, True),
     (40, 2, 12, 12, 130, 64, False),
+    (64, 16, 8, 8, 512, 100, True),   # rows of 512 elements: single tokens take four query heads a block
+    (40, 5, 12, 12, 260, None, False),
 ]
 
 
@@ -279,7 +285,7 @@ def test_one_loud_token_at_the_edges_of_what_a_query_sees(dtype, window, keep, l
     h = rand((T, C), 21, 0.3)
     h[loud] *= 50.0
     h = h.to(dtype)
-    attn_shape = (C, 2, 1, 8, 8, window, keep, 4, 100.0, "element", False)
+    attn_shape = (C, 2, 1, 16, 16, window, keep, 4, 100.0, "element", False)
     part, m, ref = attention_part(attn_shape, dtype, rt, seed=3)
     want = plain_attention(h.double(), ref, m, "element", None)
     sees = plain.visible(T, window, keep)[:, loud]
