@@ -62,7 +62,7 @@ _MIX_SIGNATURES = {
     "krk_sink_attention_single": [_P, c_int, c_int, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                                   c_int, _P, _P, c_int, c_float, c_int, c_int, _P, c_int, c_int, c_int, _P, c_int, c_int, c_float,
                                   c_int, c_int, _P, c_int, c_int, c_int, c_int, _P],
-    "krk_latent_norm_write": [_P, c_int, c_int, c_int, _P, c_float, _P, _P, _P, _P, c_int, c_int, _P, c_int, c_int, _P],
+    "krk_latent_norm_write": [_P, c_int, c_int, c_int, _P, c_float, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_int, _P],
     "krk_head_linear": [_P, c_int, c_int, c_float, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P],
 }
 _MOE_SIGNATURES = {
@@ -531,16 +531,19 @@ class Kernels:
                                         self._stream()), "gated activation")
         return out
 
-    def latent_norm_write(self, proj, c_col, rank, gain, eps, batch, cache):
-        """The rows' ``rank`` columns from ``c_col`` on, RMS-normed with a float32 gain, into the cache (one head)."""
+    def latent_norm_write(self, proj, c_col, rank, gain, eps, batch, cache, keep_rows=False):
+        """The rows' ``rank`` columns from ``c_col`` on, RMS-normed with a float32 gain, into the cache (one head);
+        with ``keep_rows`` the normalised rows are returned as well, [rows, rank]."""
         ptr, stride = self._rows_view(proj)
         if cache.k.dtype != proj.dtype or cache.head_dim != rank or cache.kv_heads != 1 or gain.dtype != torch.float32:
             raise KernelError("the cache does not fit the latent rows it is to receive")
+        kept = torch.empty((proj.shape[0], rank), dtype=proj.dtype, device=proj.device) if keep_rows else None
         self._ok(self.mix.krk_latent_norm_write(ptr, stride, int(c_col), int(rank), gain.data_ptr(), float(eps),
                                                 batch.row_seq.data_ptr(), batch.row_pos.data_ptr(),
                                                 batch.seq_slot.data_ptr(), cache.table.data_ptr(), cache.width,
                                                 int(getattr(cache, "keep_pages", 0)), cache.k.data_ptr(), proj.shape[0],
-                                                _code(proj.dtype), self._stream()), "latent norm + cache write")
+                                                _ptr(kept), _code(proj.dtype), self._stream()), "latent norm + cache write")
+        return kept
 
     def head_linear(self, x, w, out=None, out_col=0, out_scale=1.0):
         """out[r, h, :] = out_scale * W_h x[r, h, :]; W [heads, N, K] contiguous, x [rows, heads * K] (rows may be strided)."""

@@ -2,7 +2,7 @@
 //
 // krk_latent_norm_write: one warp per row. The row's `rank` projected elements are divided by their root
 // mean square (eps under the root), multiplied by a float32 gain and written, rounded once, to the
-// position's place in a cache of one "kv head" of `rank` elements.
+// position's place in a cache of one "kv head" of `rank` elements (and, if asked, to a plain row buffer as well).
 //
 // krk_head_linear: out[r, h, :] = scale * W_h x[r, h, :] for every head h, W [heads, N, K] contiguous;
 // x and out are rows with strides. One block per (tile of output elements, head, tile of 8 rows): the
@@ -16,7 +16,8 @@ template <typename T>
 __global__ void latent_norm_write_kernel(const T* __restrict__ proj, int stride, int c_col, int R,
                                          const float* __restrict__ gain, float eps, const int* __restrict__ row_seq,
                                          const int* __restrict__ row_pos, const int* __restrict__ seq_slot,
-                                         const int* __restrict__ table, int width, int keep_pages, T* cache, int rows) {
+                                         const int* __restrict__ table, int width, int keep_pages, T* cache, int rows,
+                                         T* __restrict__ rows_out) {
   grid_launch_dependents();
   grid_dependency_wait();
   const int lane = threadIdx.x & 31;
@@ -32,7 +33,11 @@ __global__ void latent_norm_write_kernel(const T* __restrict__ proj, int stride,
   const int pos = row_pos[row];
   const int page = page_of(table, width, seq_slot[row_seq[row]], pos, keep_pages);
   T* dst = cache + ((size_t)page * KRK_PAGE + (pos % KRK_PAGE)) * R;
-  for (int i = lane; i < R; i += 32) dst[i] = from_float<T>(to_float<T>(c[i]) * rstd * gain[i]);
+  for (int i = lane; i < R; i += 32) {
+    const T v = from_float<T>(to_float<T>(c[i]) * rstd * gain[i]);
+    dst[i] = v;
+    if (rows_out) rows_out[(size_t)row * R + i] = v;
+  }
 }
 
 constexpr int HL_ROWS = 8;
@@ -71,17 +76,17 @@ head_linear_kernel(T* __restrict__ out, int out_stride, int out_col, float out_s
 
 KRK_API int krk_latent_norm_write(const void* proj, int stride, int c_col, int R, const float* gain, float eps,
                                   const int* row_seq, const int* row_pos, const int* seq_slot, const int* table, int width,
-                                  int keep_pages, void* cache, int rows, int dtype, cudaStream_t stream) {
+                                  int keep_pages, void* cache, int rows, void* rows_out, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   const int warps = 4;
   const unsigned blocks = (unsigned)((rows + warps - 1) / warps);
   if (dtype == KRK_DTYPE_F32)
     return (int)launch_pdl(latent_norm_write_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, (const float*)proj,
                            stride, c_col, R, gain, eps, row_seq, row_pos, seq_slot, table, width, keep_pages,
-                           (float*)cache, rows);
+                           (float*)cache, rows, (float*)rows_out);
   return (int)launch_pdl(latent_norm_write_kernel<bf16>, dim3(blocks), dim3(warps * 32), 0, stream, (const bf16*)proj,
                          stride, c_col, R, gain, eps, row_seq, row_pos, seq_slot, table, width, keep_pages, (bf16*)cache,
-                         rows);
+                         rows, (bf16*)rows_out);
 }
 
 KRK_API int krk_head_linear(void* out, int out_stride, int out_col, float out_scale, const void* x, int x_stride,

@@ -217,6 +217,8 @@ LATENT_SHAPES = [  # hidden, heads, dim, vdim, rank, window, sink
     (40, 2, 12, 12, 130, 64, False),
     (64, 16, 8, 8, 512, 100, True),   # rows of 512 elements: single tokens take four query heads a block
     (40, 5, 12, 12, 260, None, False),
+    (64, 4, 16, 16, 40, 50, True),    # key and value heads of one size: whole prompts in bfloat16 on the tensor cores
+    (64, 2, 32, 32, 24, None, False),
 ]
 
 

@@ -205,13 +205,14 @@ class _WideOps:
             out = out * torch.sigmoid(g[:, row_gate_col:row_gate_col + 1])
         return out.to(gu.dtype)
 
-    def latent_norm_write(self, proj, c_col, rank, gain, eps, batch, cache):
+    def latent_norm_write(self, proj, c_col, rank, gain, eps, batch, cache, keep_rows=False):
         c = proj[:, c_col:c_col + rank].float()
         c = c * torch.rsqrt((c * c).mean(dim=-1, keepdim=True) + eps) * gain.float()
         pos = batch.row_pos.long()
         slot = batch.seq_slot.long()[batch.row_seq.long()]
         page = cache.table.long()[slot, _entry(cache, pos)]
         cache.k[page, 0, pos % PAGE] = c.to(proj.dtype)
+        return c.to(proj.dtype) if keep_rows else None
 
     def head_linear(self, x, w, out=None, out_col=0, out_scale=1.0):
         heads, n, k = w.shape
