@@ -66,12 +66,12 @@ _MIX_SIGNATURES = {
     "krk_head_linear": [_P, c_int, c_int, c_float, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P],
 }
 _MOE_SIGNATURES = {
-    "krk_moe_route": [_P, _P, _P, _P, c_int, c_int, c_int, _P],
+    "krk_moe_route": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
     "krk_moe_gate_up_pairs": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
-    "krk_moe_down_pairs": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "krk_moe_down_pairs": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "krk_moe_sort": [_P, _P, _P, c_int, c_int, c_int, _P],
     "krk_moe_gather": [_P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
-    "krk_moe_combine": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, _P],
+    "krk_moe_combine": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, _P],
 }
 _SCAN_SIGNATURES = {
     "krk_token_shift": [_P, _P, c_int, _P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P],
@@ -571,19 +571,24 @@ class Kernels:
     # -- routed experts ------------------------------------------------------------------------
     MOE_PAIR_ROWS = 16  # rows up to which every (row, expert) pair reads its expert's weights by itself
 
-    def moe_route(self, x, w, b, top):
-        """(experts int32 [rows, top], weights float32 [rows, top]): the ``top`` largest of x W^T + b in 32-bit
-        (ties: the lower index) and the softmax over them."""
-        logits = self.linear(x, w, out_float32=True)
-        rows, E = logits.shape
+    def moe_route(self, x, w, b, top, gate_row=False):
+        """(experts int32 [rows, top], weights float32 [rows, top], row gate float32 [rows] or None): the ``top`` largest
+        of x W^T + b in 32-bit (ties: the lower index) and the softmax over them. With ``gate_row`` the last row of W is
+        no expert but a gate's weights: sigmoid of its product is the row gate."""
+        E = w.shape[0] - int(gate_row)
+        rows, K = x.shape
         experts = torch.empty((rows, top), dtype=torch.int32, device=x.device)
         weights = torch.empty((rows, top), dtype=torch.float32, device=x.device)
-        self._ok(self.moe.krk_moe_route(experts.data_ptr(), weights.data_ptr(), logits.data_ptr(), _ptr(b), rows, E, int(top),
-                                        self._stream()), "expert routing")
-        return experts, weights
+        row_gate = torch.empty(rows, dtype=torch.float32, device=x.device) if gate_row else None
+        logits = self.linear(x, w, out_float32=True)
+        self._ok(self.moe.krk_moe_route(experts.data_ptr(), weights.data_ptr(), _ptr(row_gate), logits.data_ptr(), _ptr(b),
+                                        rows, E, int(gate_row), int(top), self._stream()), "expert routing")
+        return experts, weights, row_gate
 
-    def moe_experts(self, x, w_gate_up, w_down, experts, weights, intermediate, activation, add=None, batch=None):
-        """add + sum_j weights[r, j] * expert_{experts[r, j]}(x[r]); w_gate_up [E, 2F, K], w_down [E, C, F]."""
+    def moe_experts(self, x, w_gate_up, w_down, experts, weights, intermediate, activation, add=None, add_gate=None,
+                    batch=None):
+        """add * add_gate + sum_j weights[r, j] * expert_{experts[r, j]}(x[r]); w_gate_up [E, 2F, K], w_down [E, C, F];
+        ``add_gate``: one float32 number per row (None: 1)."""
         rows, top = experts.shape
         E, C, F = w_down.shape
         K = x.shape[1]
@@ -595,7 +600,7 @@ class Kernels:
             pairs = torch.empty((rows * top, F), dtype=x.dtype, device=x.device)
             self._ok(self.moe.krk_moe_gate_up_pairs(pairs.data_ptr(), ptr, stride, w_gate_up.data_ptr(), experts.data_ptr(),
                                                     rows, top, F, K, act, _code(x.dtype), self._stream()), "experts' gate/up")
-            self._ok(self.moe.krk_moe_down_pairs(out.data_ptr(), _ptr(add), pairs.data_ptr(), w_down.data_ptr(),
+            self._ok(self.moe.krk_moe_down_pairs(out.data_ptr(), _ptr(add), _ptr(add_gate), pairs.data_ptr(), w_down.data_ptr(),
                                                  experts.data_ptr(), weights.data_ptr(), rows, top, C, F, _code(x.dtype),
                                                  self._stream()), "experts' down")
             return out
@@ -628,7 +633,7 @@ class Kernels:
                 if b > a:
                     h = self.gate_up_act(xg[a:b], w_gate_up[e], F, activation)
                     yg[a:b] = self.linear(h, w_down[e])
-        self._ok(self.moe.krk_moe_combine(out.data_ptr(), _ptr(add), yg.data_ptr(), place.data_ptr(), experts.data_ptr(),
+        self._ok(self.moe.krk_moe_combine(out.data_ptr(), _ptr(add), _ptr(add_gate), yg.data_ptr(), place.data_ptr(), experts.data_ptr(),
                                           offsets.data_ptr(), cap, weights.data_ptr(), rows, top, C, _code(x.dtype),
                                           self._stream()), "experts' sum")
         return out

@@ -1,7 +1,11 @@
 // Kernels of a feed-forward of routed experts.
 //
 // krk_moe_route: one warp per row. z = logits[r, :] + bias (float32); the `top` largest are taken one after
-// the other (ties: the lower index), and their weights are the softmax over the chosen logits alone.
+// the other (ties: the lower index), and their weights are the softmax over the chosen logits alone. A gate of one
+// number per row may ride in the router's product as its last column: sigmoid of it is written beside the routing and
+// multiplies what the experts' sum is added onto (a shared expert's output). (The router's product inside this
+// kernel, one block per row, was measured for single-token steps and lost to the product kernel before it: 1.72
+// against 1.53 ms a step of one sequence at 64 experts of width 2,048.)
 //
 // Few rows (single-token steps): a (row, chosen expert) pair reads its expert's weights once.
 //   krk_moe_gate_up_pairs: act[pair, f] = a(Wg_e[f] . x_r) * (Wu_e[f] . x_r), a warp per f, lanes over K.
@@ -25,17 +29,10 @@ __device__ __forceinline__ float act_of(float z, int act) {
 
 constexpr int ROUTE_WARPS = 4;
 
-__global__ void moe_route_kernel(int* __restrict__ experts, float* __restrict__ weights, const float* __restrict__ logits,
-                                 const float* __restrict__ bias, int rows, int E, int top) {
-  extern __shared__ float z_s[];  // [warps][E]
-  grid_launch_dependents();
-  grid_dependency_wait();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int row = blockIdx.x * ROUTE_WARPS + warp;
-  if (row >= rows) return;
-  float* z = z_s + (size_t)warp * E;
-  for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)row * E + e] + (bias ? bias[e] : 0.f);
-  __syncwarp();
+// One warp: the `top` largest of z[0..E) one after the other (z is the warp's own shared memory and is consumed),
+// their softmax weights.
+__device__ __forceinline__ void route_row(float* z, int E, int top, int lane, int* __restrict__ experts,
+                                          float* __restrict__ weights) {
   float first = 0.f, total = 0.f, mine = 0.f;
   int mine_e = 0;
   for (int j = 0; j < top; ++j) {
@@ -59,9 +56,28 @@ __global__ void moe_route_kernel(int* __restrict__ experts, float* __restrict__ 
     __syncwarp();
   }
   if (lane < top) {
-    experts[(size_t)row * top + lane] = mine_e;
-    weights[(size_t)row * top + lane] = mine / total;
+    experts[lane] = mine_e;
+    weights[lane] = mine / total;
   }
+}
+
+// logits [rows, E + has_gate]: the last column, if there is one, is a gate's logit of the row (it rides in the router's
+// product), and sigmoid of it goes to row_gate
+__global__ void moe_route_kernel(int* __restrict__ experts, float* __restrict__ weights, float* __restrict__ row_gate,
+                                 const float* __restrict__ logits, const float* __restrict__ bias, int rows, int E,
+                                 int has_gate, int top) {
+  extern __shared__ float z_s[];  // [warps][E]
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x * ROUTE_WARPS + warp;
+  if (row >= rows) return;
+  float* z = z_s + (size_t)warp * E;
+  const float* src = logits + (size_t)row * (E + has_gate);
+  for (int e = lane; e < E; e += 32) z[e] = src[e] + (bias ? bias[e] : 0.f);
+  if (has_gate && lane == 0) row_gate[row] = act_of(src[E], 2);
+  __syncwarp();
+  route_row(z, E, top, lane, experts + (size_t)row * top, weights + (size_t)row * top);
 }
 
 constexpr int PAIR_WARPS = 8;
@@ -92,7 +108,7 @@ moe_gate_up_pairs_kernel(T* __restrict__ act_out, const T* __restrict__ x, int x
 
 template <typename T>
 __global__ void __launch_bounds__(PAIR_WARPS * 32)
-moe_down_pairs_kernel(T* __restrict__ out, const T* __restrict__ add, const T* __restrict__ act_in,
+moe_down_pairs_kernel(T* __restrict__ out, const T* __restrict__ add, const float* __restrict__ add_gate, const T* __restrict__ act_in,
                       const T* __restrict__ w, const int* __restrict__ experts, const float* __restrict__ weights, int top,
                       int C, int F) {
   extern __shared__ __align__(16) float as[];  // [top][F4], F4 = F rounded up to a multiple of 4
@@ -104,7 +120,7 @@ moe_down_pairs_kernel(T* __restrict__ out, const T* __restrict__ add, const T* _
   for (int i = threadIdx.x; i < top * F; i += blockDim.x) as[(i / F) * F4 + i % F] = to_float<T>(act_in[(size_t)row * top * F + i]);
   __syncthreads();
   for (int c = blockIdx.x * PAIR_WARPS + warp; c < C; c += gridDim.x * PAIR_WARPS) {
-    float total = add ? to_float<T>(add[(size_t)row * C + c]) : 0.f;
+    float total = add ? to_float<T>(add[(size_t)row * C + c]) * (add_gate ? add_gate[row] : 1.f) : 0.f;
     for (int j = 0; j < top; ++j) {
       const int e = experts[(size_t)row * top + j];
       const T* wr = w + ((size_t)e * C + c) * F;
@@ -167,7 +183,7 @@ __global__ void moe_gather_kernel(T* __restrict__ xg, const T* __restrict__ x, i
 }
 
 template <typename T>
-__global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ add, const T* __restrict__ yg,
+__global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ add, const float* __restrict__ add_gate, const T* __restrict__ yg,
                                    const int* __restrict__ place, const int* __restrict__ experts,
                                    const int* __restrict__ offsets, int cap, const float* __restrict__ weights, int top,
                                    int C) {
@@ -181,7 +197,7 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ ad
   }
   __syncthreads();
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float total = add ? to_float<T>(add[(size_t)row * C + c]) : 0.f;
+    float total = add ? to_float<T>(add[(size_t)row * C + c]) * (add_gate ? add_gate[row] : 1.f) : 0.f;
     for (int j = 0; j < top; ++j) total += src_w[j] * to_float<T>(yg[(size_t)src_row[j] * C + c]);
     out[(size_t)row * C + c] = from_float<T>(total);
   }
@@ -189,14 +205,14 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ ad
 
 }  // namespace
 
-KRK_API int krk_moe_route(int* experts, float* weights, const float* logits, const float* bias, int rows, int E, int top,
-                          cudaStream_t stream) {
+KRK_API int krk_moe_route(int* experts, float* weights, float* row_gate, const float* logits, const float* bias, int rows,
+                          int E, int has_gate, int top, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (top < 1 || top > 32 || top > E) return -2;
   const size_t smem = (size_t)ROUTE_WARPS * E * sizeof(float);
   if (smem > 48 * 1024) return -2;
   return (int)launch_pdl(moe_route_kernel, dim3((rows + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream,
-                         experts, weights, logits, bias, rows, E, top);
+                         experts, weights, row_gate, logits, bias, rows, E, has_gate, top);
 }
 
 KRK_API int krk_moe_gate_up_pairs(void* act_out, const void* x, int x_stride, const void* w, const int* experts, int rows,
@@ -212,7 +228,7 @@ KRK_API int krk_moe_gate_up_pairs(void* act_out, const void* x, int x_stride, co
                          (const bf16*)x, x_stride, (const bf16*)w, experts, top, F, K, act);
 }
 
-KRK_API int krk_moe_down_pairs(void* out, const void* add, const void* act_in, const void* w, const int* experts,
+KRK_API int krk_moe_down_pairs(void* out, const void* add, const float* add_gate, const void* act_in, const void* w, const int* experts,
                                const float* weights, int rows, int top, int C, int F, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   const size_t smem = (size_t)top * ((F + 3) & ~3) * sizeof(float);
@@ -220,9 +236,9 @@ KRK_API int krk_moe_down_pairs(void* out, const void* add, const void* act_in, c
   const dim3 grid((unsigned)min((C + PAIR_WARPS - 1) / PAIR_WARPS, 1024), (unsigned)rows);
   if (dtype == KRK_DTYPE_F32)
     return (int)launch_pdl(moe_down_pairs_kernel<float>, grid, dim3(PAIR_WARPS * 32), smem, stream, (float*)out,
-                           (const float*)add, (const float*)act_in, (const float*)w, experts, weights, top, C, F);
+                           (const float*)add, add_gate, (const float*)act_in, (const float*)w, experts, weights, top, C, F);
   return (int)launch_pdl(moe_down_pairs_kernel<bf16>, grid, dim3(PAIR_WARPS * 32), smem, stream, (bf16*)out,
-                         (const bf16*)add, (const bf16*)act_in, (const bf16*)w, experts, weights, top, C, F);
+                         (const bf16*)add, add_gate, (const bf16*)act_in, (const bf16*)w, experts, weights, top, C, F);
 }
 
 KRK_API int krk_moe_sort(int* offsets, int* place, const int* experts, int rows, int top, int E, cudaStream_t stream) {
@@ -242,14 +258,14 @@ KRK_API int krk_moe_gather(void* xg, const void* x, int x_stride, const int* pla
                          place, experts, offsets, cap, top, K);
 }
 
-KRK_API int krk_moe_combine(void* out, const void* add, const void* yg, const int* place, const int* experts,
+KRK_API int krk_moe_combine(void* out, const void* add, const float* add_gate, const void* yg, const int* place, const int* experts,
                             const int* offsets, int cap, const float* weights, int rows, int top, int C, int dtype,
                             cudaStream_t stream) {
   if (rows == 0) return 0;
   if (top > 32) return -2;
   if (dtype == KRK_DTYPE_F32)
-    return (int)launch_pdl(moe_combine_kernel<float>, dim3(rows), dim3(256), 0, stream, (float*)out, (const float*)add,
+    return (int)launch_pdl(moe_combine_kernel<float>, dim3(rows), dim3(256), 0, stream, (float*)out, (const float*)add, add_gate,
                            (const float*)yg, place, experts, offsets, cap, weights, top, C);
-  return (int)launch_pdl(moe_combine_kernel<bf16>, dim3(rows), dim3(256), 0, stream, (bf16*)out, (const bf16*)add,
+  return (int)launch_pdl(moe_combine_kernel<bf16>, dim3(rows), dim3(256), 0, stream, (bf16*)out, (const bf16*)add, add_gate,
                          (const bf16*)yg, place, experts, offsets, cap, weights, top, C);
 }

@@ -252,11 +252,14 @@ sink_attention_single_kernel(T* __restrict__ out, int out_stride, int out_col, f
                              const float* __restrict__ sink, const int* __restrict__ seq_slot,
                              const int* __restrict__ seq_start, const int* __restrict__ table, int width,
                              const T* __restrict__ k_cache, const T* __restrict__ v_cache, float scale, int window,
-                             int g0, int GN, int SPL, float* __restrict__ scratch, int k_col, int v_col,
+                             int SPL, float* __restrict__ scratch, int k_col, int v_col,
                              const float* __restrict__ inv_freq, int rot, int value_norm, float eps, T* k_cache_w,
                              T* v_cache_w, int keep_first, int keep_pages, const T* __restrict__ gate, int gate_stride,
                              int gate_col, int gate_mode) {
   extern __shared__ __align__(16) float sm1[];
+  // a kv head's query heads are served GM at a time: blockIdx.y picks the group, all groups in one launch
+  const int g0 = blockIdx.y * GM;
+  const int GN = min(GM, HQ / HKV - g0);
   float* q_s = sm1;                       // [GN][D]
   float* part = q_s + GN * D;             // [warps][GN][DV + 2]
   // fused form: the new token's rotated key and normalised value, as the cache stores them
@@ -593,8 +596,9 @@ KRK_API int krk_sink_attention_single(void* out, int out_stride, int out_col, fl
   const int gm = wide ? 4 : GROUP_MAX;
   if (fuse && (wide || G > GROUP_MAX)) return -2;  // the new key and value are made by one launch per item
   if (fuse && (rot < 0 || rot > D || (rot & 1))) return -2;
-  for (int g0 = 0; g0 < G; g0 += gm) {
-    const int GN = min(gm, G - g0);
+  {
+    const int GN = min(gm, G);  // the most heads a block serves; blocks of the last group may serve fewer
+    const int groups = (G + gm - 1) / gm;
     const size_t esz = dtype == KRK_DTYPE_F32 ? 4 : 2;
     const size_t smem = ((size_t)GN * D + (size_t)SINGLE_WARPS * GN * (DV + 2) + 4) * sizeof(float) +
                         (((size_t)D + 7) / 8 * 8 + DV + 8) * esz;
@@ -606,9 +610,9 @@ KRK_API int krk_sink_attention_single(void* out, int out_stride, int out_col, fl
                   : fuse ? (v4 ? sink_attention_single_kernel<float, true, true, 4, GROUP_MAX> : sink_attention_single_kernel<float, false, true, 4, GROUP_MAX>)
                          : (v4 ? sink_attention_single_kernel<float, true, false, 4, GROUP_MAX> : sink_attention_single_kernel<float, false, false, 4, GROUP_MAX>);
       if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-      e = launch_pdl(kern, dim3(n_seqs * HKV * SPL), dim3(SINGLE_WARPS * 32), smem, stream,
+      e = launch_pdl(kern, dim3(n_seqs * HKV * SPL, groups), dim3(SINGLE_WARPS * 32), smem, stream,
                      (float*)out, out_stride, out_col, out_scale, (const float*)proj, stride, q_col, HQ, HKV, D, DV, sink,
-                     seq_slot, seq_start, table, width, (const float*)k_cache, (const float*)v_cache, scale, window, g0, GN, SPL, scratch, k_col, v_col,
+                     seq_slot, seq_start, table, width, (const float*)k_cache, (const float*)v_cache, scale, window, SPL, scratch, k_col, v_col,
                      inv_freq, rot, value_norm, eps, (float*)k_cache, (float*)v_cache, keep_first, keep_pages,
                      (const float*)gate, gate_stride, gate_col, gate_mode);
     } else {
@@ -616,9 +620,9 @@ KRK_API int krk_sink_attention_single(void* out, int out_stride, int out_col, fl
                   : fuse ? (v4 ? sink_attention_single_kernel<bf16, true, true, 4, GROUP_MAX> : sink_attention_single_kernel<bf16, false, true, 4, GROUP_MAX>)
                          : (v4 ? sink_attention_single_kernel<bf16, true, false, 4, GROUP_MAX> : sink_attention_single_kernel<bf16, false, false, 4, GROUP_MAX>);
       if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-      e = launch_pdl(kern, dim3(n_seqs * HKV * SPL), dim3(SINGLE_WARPS * 32), smem, stream,
+      e = launch_pdl(kern, dim3(n_seqs * HKV * SPL, groups), dim3(SINGLE_WARPS * 32), smem, stream,
                      (bf16*)out, out_stride, out_col, out_scale, (const bf16*)proj, stride, q_col, HQ, HKV, D, DV, sink,
-                     seq_slot, seq_start, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale, window, g0, GN, SPL, scratch, k_col, v_col,
+                     seq_slot, seq_start, table, width, (const bf16*)k_cache, (const bf16*)v_cache, scale, window, SPL, scratch, k_col, v_col,
                      inv_freq, rot, value_norm, eps, (bf16*)k_cache, (bf16*)v_cache, keep_first, keep_pages,
                      (const bf16*)gate, gate_stride, gate_col, gate_mode);
     }

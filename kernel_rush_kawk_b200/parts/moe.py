@@ -9,10 +9,12 @@ one number per token, before it is added.
 
 The routing never leaves the device: a routing kernel writes each row's experts and
 weights; few rows (single-token steps) read each chosen expert's weights once per
-(row, expert) pair; many rows are counted, ordered by expert and multiplied expert by
-expert in tiles. The shared expert is one stacked product [gate; up; sg], an
-activation that also applies the token's sigmoid, and a down product whose result the
-routed sum is added onto.
+(row, expert) pair; many rows are counted, ordered by expert and multiplied by all
+experts in one batched product. The shared expert is a gated feed-forward of its own
+(stacked [gate; up] product with the activation, a down product); its gate's weights
+ride in the router's product as one more row, the routing kernel writes the token's
+sigmoid beside the routing, and the kernel that adds the experts' weighted results
+onto the shared expert's output multiplies that output by it.
 """
 
 from __future__ import annotations
@@ -20,7 +22,6 @@ from __future__ import annotations
 import torch
 
 from .base import FeedForward, TensorSpec, register_feed_forward
-from .branches import pad_rows
 
 
 class RoutedExperts(FeedForward):
@@ -59,14 +60,14 @@ class RoutedExperts(FeedForward):
 
     def bind(self, tensors, runtime):
         E = self.experts
-        self.router_w = tensors["router"].contiguous()  # in the path's dtype: the logits' product accumulates in 32-bit
+        # in the path's dtype: the logits' product accumulates in 32-bit; the shared expert's gate is its last row
+        self.router_w = torch.cat([tensors["router"]] + ([tensors["shared.sg"]] if self.shared_gate else []), dim=0).contiguous()
         self.router_b = tensors["router.b"].float().contiguous()
         self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0) for e in range(E)]).contiguous()
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(E)]).contiguous()
         self.w_shared_in = self.w_shared_down = None
         if self.shared is not None:
-            rows = [tensors["shared.gate"], tensors["shared.up"]] + ([tensors["shared.sg"]] if self.shared_gate else [])
-            self.w_shared_in = pad_rows(torch.cat(rows, dim=0))
+            self.w_shared_in = torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0).contiguous()
             self.w_shared_down = tensors["shared.down"].contiguous()
 
     def forward(self, ctx, h):
@@ -74,12 +75,10 @@ class RoutedExperts(FeedForward):
         x = h.tensor() if hasattr(h, "tensor") and not isinstance(h, torch.Tensor) else h
         base = None
         if self.shared is not None:
-            su = ops.linear(x, self.w_shared_in)
-            act = ops.gated_act(su, self.shared, self.activation, row_gate_col=2 * self.shared if self.shared_gate else None)
-            base = ops.linear(act, self.w_shared_down)
-        experts, weights = ops.moe_route(x, self.router_w, self.router_b, self.top)
+            base = ops.linear(ops.gate_up_act(x, self.w_shared_in, self.shared, self.activation), self.w_shared_down)
+        experts, weights, row_gate = ops.moe_route(x, self.router_w, self.router_b, self.top, gate_row=self.shared_gate)
         return ops.moe_experts(x, self.w_gate_up, self.w_down, experts, weights, self.intermediate, self.activation,
-                               add=base, batch=ctx.batch)
+                               add=base, add_gate=row_gate, batch=ctx.batch)
 
 
 register_feed_forward("routed_experts", RoutedExperts)

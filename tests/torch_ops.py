@@ -223,14 +223,19 @@ class _WideOps:
         out[:, out_col:out_col + heads * n] = y.to(out.dtype)
         return out
 
-    def moe_route(self, x, w, b, top):
-        z = x.float() @ w.float().t() + b.float()
+    def moe_route(self, x, w, b, top, gate_row=False):
+        z = x.float() @ w.float().t()
+        row_gate = torch.sigmoid(z[:, -1]) if gate_row else None
+        z = (z[:, :-1] if gate_row else z) + b.float()
         best = torch.topk(z, top, dim=-1)  # ties are not exercised: equal logits do not occur with random weights
-        return best.indices.to(torch.int32), torch.softmax(best.values, dim=-1)
+        return best.indices.to(torch.int32), torch.softmax(best.values, dim=-1), row_gate
 
-    def moe_experts(self, x, w_gate_up, w_down, experts, weights, intermediate, activation, add=None, batch=None):
+    def moe_experts(self, x, w_gate_up, w_down, experts, weights, intermediate, activation, add=None, add_gate=None,
+                    batch=None):
         rows, top = experts.shape
         out = torch.zeros((rows, w_down.shape[1]), dtype=torch.float32) if add is None else add.float().clone()
+        if add is not None and add_gate is not None:
+            out = out * add_gate[:, None]
         xf = x.float()
         for r in range(rows):
             for j in range(top):
