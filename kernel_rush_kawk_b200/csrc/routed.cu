@@ -121,11 +121,40 @@ moe_down_pairs_kernel(T* __restrict__ out, const T* __restrict__ add, const floa
   __syncthreads();
   for (int c = blockIdx.x * PAIR_WARPS + warp; c < C; c += gridDim.x * PAIR_WARPS) {
     float total = add ? to_float<T>(add[(size_t)row * C + c]) * (add_gate ? add_gate[row] : 1.f) : 0.f;
-    for (int j = 0; j < top; ++j) {
-      const int e = experts[(size_t)row * top + j];
-      const T* wr = w + ((size_t)e * C + c) * F;
-      const float s = warp_sum(lane_dot<T>(wr, as + j * F4, F, lane));
-      total += weights[(size_t)row * top + j] * round_to<T>(s);
+    // four experts' rows are read side by side, so that four times the bytes are in flight; the results are still
+    // added in the order of the choice
+    for (int j0 = 0; j0 < top; j0 += 4) {
+      const T* wr[4];
+      float s[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int j = min(j0 + jj, top - 1);
+        wr[jj] = w + ((size_t)experts[(size_t)row * top + j] * C + c) * F;
+        s[jj] = 0.f;
+      }
+      if (sizeof(T) == 2 && (F & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+        for (int k = lane * 8; k < F; k += 256) {
+          uint4 raw[4];
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) raw[jj] = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(wr[jj]) + k);
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const float* xs = as + min(j0 + jj, top - 1) * F4 + k;
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[jj]);
+            const float4 a = *reinterpret_cast<const float4*>(xs), b = *reinterpret_cast<const float4*>(xs + 4);
+            s[jj] += __low2float(p[0]) * a.x + __high2float(p[0]) * a.y + __low2float(p[1]) * a.z + __high2float(p[1]) * a.w +
+                     __low2float(p[2]) * b.x + __high2float(p[2]) * b.y + __low2float(p[3]) * b.z + __high2float(p[3]) * b.w;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) s[jj] = lane_dot<T>(wr[jj], as + min(j0 + jj, top - 1) * F4, F, lane);
+      }
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const float r = warp_sum(s[jj]);
+        if (j0 + jj < top) total += weights[(size_t)row * top + j0 + jj] * round_to<T>(r);
+      }
     }
     if (lane == 0) out[(size_t)row * C + c] = from_float<T>(total);
   }

@@ -505,23 +505,33 @@ __global__ void sink_attention_merge_kernel(T* __restrict__ out, int out_stride,
   if (w >= (long long)n_items * G) return;
   const int item = (int)(w / G), g = (int)(w % G);
   const int seq = item / HKV, kh = item % HKV;
+  // at most 8 blocks share an item: their maxima, then one factor each, then the shares added in block order
+  const float* base = scratch + ((size_t)item * SPL * G + g) * PS;
+  const size_t step = (size_t)G * PS;
+  float ms[8], f[8];
   float mx = -INFINITY;
-  for (int sp = 0; sp < SPL; ++sp) mx = fmaxf(mx, scratch[(((size_t)item * SPL + sp) * G + g) * PS + DV]);
+#pragma unroll
+  for (int sp = 0; sp < 8; ++sp) {
+    ms[sp] = sp < SPL ? base[sp * step + DV] : -INFINITY;
+    mx = fmaxf(mx, ms[sp]);
+  }
   float total = 0.f;
-  for (int sp = 0; sp < SPL; ++sp) {
-    const float* src = scratch + (((size_t)item * SPL + sp) * G + g) * PS;
-    total += src[DV] == -INFINITY ? 0.f : src[DV + 1] * expf(src[DV] - mx);
+#pragma unroll
+  for (int sp = 0; sp < 8; ++sp) {
+    f[sp] = ms[sp] == -INFINITY ? 0.f : expf(ms[sp] - mx);
+    if (sp < SPL) total += base[sp * step + DV + 1] * f[sp];
   }
   T* op = out + (size_t)seq * out_stride + out_col + (size_t)(kh * G + g) * DV;
   float inv = out_scale / total;
   const T* gp = gate_mode ? gate + (size_t)seq * gate_stride + gate_col : nullptr;
   if (gate_mode == 1) inv *= sigmoidf_(to_float<T>(gp[kh * G + g]));
-  for (int d = lane; d < DV; d += 32) {  // value rows of any width; the shares are added in block order
+  for (int d = lane; d < DV; d += 32) {  // value rows of any width
+    float v[8];
+#pragma unroll
+    for (int sp = 0; sp < 8; ++sp) v[sp] = sp < SPL ? base[sp * step + d] : 0.f;
     float o = 0.f;
-    for (int sp = 0; sp < SPL; ++sp) {
-      const float* src = scratch + (((size_t)item * SPL + sp) * G + g) * PS;
-      if (src[DV] != -INFINITY) o += src[d] * expf(src[DV] - mx);
-    }
+#pragma unroll
+    for (int sp = 0; sp < 8; ++sp) o += v[sp] * f[sp];
     op[d] = from_float<T>(o * inv * (gate_mode == 2 ? sigmoidf_(to_float<T>(gp[(size_t)(kh * G + g) * DV + d])) : 1.f));
   }
 }
@@ -592,6 +602,7 @@ KRK_API int krk_sink_attention_single(void* out, int out_stride, int out_col, fl
   if (DV > 512 || D > 1024) return -2;
   const int G = HQ / HKV;
   const int SPL = (splits > 1 && scratch) ? splits : 1;
+  if (SPL > 8) return -2;  // the merge kernel holds one factor per block of an item
   const bool wide = DV > 32 * (MAX_V_PER_LANE / 2);  // value rows beyond 128 elements: fewer heads a block
   const int gm = wide ? 4 : GROUP_MAX;
   if (fuse && (wide || G > GROUP_MAX)) return -2;  // the new key and value are made by one launch per item
