@@ -93,7 +93,11 @@ KRK_API int krk_head_linear(void* out, int out_stride, int out_col, float out_sc
                             const void* w, int heads, int N, int K, int rows, int dtype, cudaStream_t stream) {
   if (rows == 0 || heads == 0 || N == 0) return 0;
   const size_t smem = (size_t)HL_ROWS * ((K + 3) & ~3) * sizeof(float);
-  if (smem > 48 * 1024) return -2;
+  if (smem > 200 * 1024) return -2;
+  if (smem > 48 * 1024) {
+    cudaFuncSetAttribute(head_linear_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(head_linear_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
   const int row_tiles = (rows + HL_ROWS - 1) / HL_ROWS;
   if (heads > 65535 || row_tiles > 65535) return -3;
   const dim3 grid((unsigned)((N + HL_WARPS - 1) / HL_WARPS), (unsigned)heads, (unsigned)row_tiles);

@@ -248,7 +248,11 @@ KRK_API int krk_moe_gate_up_pairs(void* act_out, const void* x, int x_stride, co
                                   int top, int F, int K, int act, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   const size_t smem = (size_t)K * sizeof(float);
-  if (smem > 48 * 1024 || (long long)rows * top > 65535) return -2;
+  if (smem > 200 * 1024 || (long long)rows * top > 65535) return -2;
+  if (smem > 48 * 1024) {
+    cudaFuncSetAttribute(moe_gate_up_pairs_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(moe_gate_up_pairs_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
   const dim3 grid((unsigned)min((F + PAIR_WARPS - 1) / PAIR_WARPS, 1024), (unsigned)(rows * top));
   if (dtype == KRK_DTYPE_F32)
     return (int)launch_pdl(moe_gate_up_pairs_kernel<float>, grid, dim3(PAIR_WARPS * 32), smem, stream, (float*)act_out,
@@ -261,7 +265,11 @@ KRK_API int krk_moe_down_pairs(void* out, const void* add, const float* add_gate
                                const float* weights, int rows, int top, int C, int F, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   const size_t smem = (size_t)top * ((F + 3) & ~3) * sizeof(float);
-  if (smem > 48 * 1024 || rows > 65535) return -2;
+  if (smem > 200 * 1024 || rows > 65535) return -2;
+  if (smem > 48 * 1024) {  // many or wide experts a token: the block's copy of their activations needs the opt-in size
+    cudaFuncSetAttribute(moe_down_pairs_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(moe_down_pairs_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
   const dim3 grid((unsigned)min((C + PAIR_WARPS - 1) / PAIR_WARPS, 1024), (unsigned)rows);
   if (dtype == KRK_DTYPE_F32)
     return (int)launch_pdl(moe_down_pairs_kernel<float>, grid, dim3(PAIR_WARPS * 32), smem, stream, (float*)out,

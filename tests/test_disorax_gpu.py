@@ -306,6 +306,7 @@ def test_one_loud_token_at_the_edges_of_what_a_query_sees(dtype, window, keep, l
 
 MOE_SHAPES = [  # hidden, experts, top, ff, shared ff
     (64, 5, 2, 40, 24), (96, 8, 1, 48, None), (50, 3, 3, 11, 7), (64, 16, 4, 32, 64), (32, 2, 2, 16, 8),
+    (32, 9, 8, 1800, None),  # eight wide experts a token: their activations take the opt-in shared memory size
 ]
 
 
