@@ -304,6 +304,19 @@ def test_one_loud_token_at_the_edges_of_what_a_query_sees(dtype, window, keep, l
             close(run_part(part, rt, h, pieces, dtype, step_tokens=512), want, dtype, f"latent window {window} loud {loud}, pieces {pieces[:3]}")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [24, 33])
+def test_gated_activation_with_a_gate_of_one_number_per_row(dtype, inter):
+    """act(g) * u times the sigmoid of one more column of the same row (a gate that rides in the same product)."""
+    rt = runtime(dtype)
+    gu = rand((9, 2 * inter + 8), 2, 1.5).to(dtype)
+    got = rt.ops.gated_act(gu.cuda(), inter, "silu", row_gate_col=2 * inter)
+    g = gu.double()
+    want = plain.silu(g[:, :inter]) * g[:, inter:2 * inter] * torch.sigmoid(g[:, 2 * inter:2 * inter + 1])
+    close(got, want, dtype, "gated activation with a row gate")
+    close(rt.ops.gated_act(gu.cuda(), inter, "silu"), plain.silu(g[:, :inter]) * g[:, inter:2 * inter], dtype, "without")
+
+
 MOE_SHAPES = [  # hidden, experts, top, ff, shared ff
     (64, 5, 2, 40, 24), (96, 8, 1, 48, None), (50, 3, 3, 11, 7), (64, 16, 4, 32, 64), (32, 2, 2, 16, 8),
     (32, 9, 8, 1800, None),  # eight wide experts a token: their activations take the opt-in shared memory size
